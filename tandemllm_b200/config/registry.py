@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration reader and its model.
 
-A model folder's family is chosen by its own config.json (`architectures` first, then `model_type`,
+A model folder's family is chosen by its own config.json (`architectures` or `architecture` first, then `model_type`,
 top level or under `text_config`), never by a file name; an unknown one is refused with the list of
 registered names (engine/models/__init__.py:29-114 in the reference). An entry holds two callables:
 
@@ -45,6 +45,8 @@ def unregister(name: str) -> None:
 
 def architecture_of(raw: dict) -> Architecture:
     names = [str(a) for a in (raw.get("architectures") or [])]
+    if isinstance(raw.get("architecture"), str):        # some families name themselves with one string
+        names.append(raw["architecture"])
     types = [str(raw.get("model_type", "")), str((raw.get("text_config") or {}).get("model_type", ""))]
     for arch in REGISTRY.values():
         if any(a in arch.architectures for a in names) or any(t in arch.model_types for t in types if t):

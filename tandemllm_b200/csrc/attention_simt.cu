@@ -25,6 +25,11 @@ constexpr int MAX_HEAD_DIM = 256;
 // and its warps then take a head each in turn. The row's rotation angles are computed once a block.
 constexpr int QK_GROUP_FLOATS = 8192;
 
+// `flags` of the q/k kernel: q and k are brought to unit root mean square although they have no norm weights; the row
+// holds no value heads, the values are the keys as projected (stored before their norm).
+#define TL_QK_UNIT_NORM 1
+#define TL_QK_VALUES_ARE_KEYS 2
+
 // DS: the head size when it is 64 or 128 and the whole head is rotated (a lane then owns DS / 64 pairs (f, f + DS / 2), its
 // weights and its angles for all heads, and the loops unroll), else 0 (any size, any rotary part).
 template <typename T, int DS>
@@ -33,7 +38,7 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
     float eps, const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ positions,
     const int* __restrict__ req_of_row, const int* __restrict__ block_table, int max_pages, int page_size, int num_pages,
     T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache, T* __restrict__ k_out,
-    T* __restrict__ v_out, int Hq, int Hk, int D, int heads_per_block, int* __restrict__ status) {
+    T* __restrict__ v_out, int Hq, int Hk, int D, int heads_per_block, int flags, int* __restrict__ status) {
   __shared__ __align__(16) float vec[QK_GROUP_FLOATS];
   __shared__ float s_sin[MAX_HEAD_DIM / 2], s_cos[MAX_HEAD_DIM / 2];
   chain_next();
@@ -41,7 +46,8 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x;
   const int head0 = blockIdx.y * heads_per_block;
-  const int n_heads = min(heads_per_block, Hq + 2 * Hk - head0);
+  const bool unit_norm = flags & TL_QK_UNIT_NORM, keys_are_values = flags & TL_QK_VALUES_ARE_KEYS;
+  const int n_heads = min(heads_per_block, Hq + (keys_are_values ? 1 : 2) * Hk - head0);
   const int pos = positions[r];
   // sincosf of a large argument is a hundred instructions, and the angles are the same for all heads of the row
   if (inv_freq && (int)threadIdx.x < rotary_dim / 2)
@@ -113,7 +119,16 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
         dst = (is_k ? k_out : v_out) + ((long long)r * Hk + kvh) * DS;
       }
       if (is_q || is_k) {
-        const float inv = (is_q ? q_weight : k_weight) ? rsqrtf(ss / (float)DS + eps) : 1.f;
+        const float inv = ((is_q ? q_weight : k_weight) || unit_norm) ? rsqrtf(ss / (float)DS + eps) : 1.f;
+        if (is_k && keys_are_values) {
+          // the value is the key as it was projected, before its norm
+          T* vdst = k_cache ? v_cache + (kv_at + (long long)kvh * page_size) * DS : v_out + ((long long)r * Hk + kvh) * DS;
+#pragma unroll
+          for (int p = 0; p < PAIRS; ++p) {
+            vdst[lane + 32 * p] = from_f32<T>(a[p]);
+            vdst[lane + 32 * p + HALF] = from_f32<T>(b2[p]);
+          }
+        }
 #pragma unroll
         for (int p = 0; p < PAIRS; ++p) {
           const int f = lane + 32 * p;
@@ -153,7 +168,11 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(
     }
     if (is_q || is_k) {
       const float* w = is_q ? q_weight : k_weight;
-      const float inv = w ? rsqrtf(ss / (float)D + eps) : 1.f;
+      const float inv = (w || unit_norm) ? rsqrtf(ss / (float)D + eps) : 1.f;
+      if (is_k && keys_are_values) {
+        T* vdst = k_cache ? v_cache + (kv_at + (long long)kvh * page_size) * D : v_out + ((long long)r * Hk + kvh) * D;
+        for (int i = lane; i < D; i += 32) vdst[i] = from_f32<T>(x[i]);
+      }
       const int half = inv_freq ? rotary_dim / 2 : 0;
       for (int f = lane; f < half; f += 32) {          // a lane rotates the pair (f, f + half)
         const float a = x[f] * inv * (w ? w[f] : 1.f), b2 = x[f + half] * inv * (w ? w[f + half] : 1.f);
@@ -276,26 +295,28 @@ static int check_heads(const char* what, int Hq, int Hk, int D) {
 extern "C" int tl_qk_prepare(const void* qkv, long long ld_qkv, const float* q_weight, const float* k_weight, float eps,
                              const float* inv_freq, int rotary_dim, const int* positions, const int* req_of_row,
                              const int* block_table, int max_pages, int page_size, int num_pages, void* q_out, void* k_cache,
-                             void* v_cache, void* k_out, void* v_out, int rows, int Hq, int Hk, int D, int dtype,
+                             void* v_cache, void* k_out, void* v_out, int rows, int Hq, int Hk, int D, int dtype, int flags,
                              int* status, cudaStream_t stream) {
   if (rows == 0) return 0;
-  if (int e = check_heads("qk_prepare", Hq, Hk, D)) return e;
+  TL_REQUIRE(Hq > 0 && Hk > 0 && Hq % Hk == 0 && D >= 1 && D <= MAX_HEAD_DIM, "qk_prepare: %d query heads, %d KV heads of size %d",
+             Hq, Hk, D);
+  const int kv_sets = (flags & TL_QK_VALUES_ARE_KEYS) ? 1 : 2;
   TL_REQUIRE(!inv_freq || (rotary_dim > 0 && rotary_dim <= D && rotary_dim % 2 == 0),
              "qk_prepare: rotary size %d for head size %d", rotary_dim, D);
   TL_REQUIRE((k_cache && v_cache && page_size > 0 && max_pages > 0) || (k_out && v_out),
              "qk_prepare: neither cache pages nor plain outputs for k and v");
   // a decode step's few rows: a few heads a block, so that a row's heads run side by side and not twelve after one another a warp
-  int heads_per_block = max(1, min(Hq + 2 * Hk, QK_GROUP_FLOATS / D));
+  int heads_per_block = max(1, min(Hq + kv_sets * Hk, QK_GROUP_FLOATS / D));
   if (rows <= 64 && heads_per_block > 8) heads_per_block = 8;
-  dim3 grid(rows, ceil_div(Hq + 2 * Hk, heads_per_block));
-  TL_REQUIRE(grid.y <= 65535, "qk_prepare: %d heads exceed the grid limit", Hq + 2 * Hk);
+  dim3 grid(rows, ceil_div(Hq + kv_sets * Hk, heads_per_block));
+  TL_REQUIRE(grid.y <= 65535, "qk_prepare: %d heads exceed the grid limit", Hq + kv_sets * Hk);
   // the unrolled form: the whole head is rotated (or nothing is) and a lane's pairs are (f, f + D / 2)
   const int ds = (!inv_freq || rotary_dim == D) && (D == 64 || D == 128) ? D : 0;
   cudaError_t e;
 #define TL_QK(T_, DS_)                                                                                                     \
   e = launch_chained(qk_prepare_kernel<T_, DS_>, grid, dim3(128), 0, stream, (const T_*)qkv, ld_qkv, q_weight, k_weight, eps, \
                      inv_freq, rotary_dim, positions, req_of_row, block_table, max_pages, page_size, num_pages, (T_*)q_out,  \
-                     (T_*)k_cache, (T_*)v_cache, (T_*)k_out, (T_*)v_out, Hq, Hk, D, heads_per_block, status)
+                     (T_*)k_cache, (T_*)v_cache, (T_*)k_out, (T_*)v_out, Hq, Hk, D, heads_per_block, flags, status)
   if (dtype == TL_FP32) {
     if (ds == 64) TL_QK(float, 64);
     else if (ds == 128) TL_QK(float, 128);

@@ -148,7 +148,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 #define TL_ACT_GELU 2        // the exact form: x * 0.5 * (1 + erf(x / sqrt(2)))
 #define TL_ACT_RELU2 3       // max(x, 0)^2
 #define TL_ACT_IDENTITY 4    // gate * up
-#define TL_ACT_LAST 4
+#define TL_ACT_XIELU 5       // a0 z^2 + z / 2 for z > 0, a1 (exp(z) - 1 - z) + z / 2 else; a0, a1 travel beside the code
+#define TL_ACT_LAST 5
 
 __device__ __forceinline__ float gate_activation(float g, int act) {
   switch (act) {
@@ -157,6 +158,11 @@ __device__ __forceinline__ float gate_activation(float g, int act) {
     case TL_ACT_IDENTITY: return g;
     default: return g / (1.f + expf(-g));
   }
+}
+// An activation with up to two constants of its own (`a0`, `a1`; the codes above that have none ignore them).
+__device__ __forceinline__ float activation(float z, int act, float a0, float a1) {
+  if (act == TL_ACT_XIELU) return z > 0.f ? fmaf(a0 * z, z, 0.5f * z) : fmaf(a1, expm1f(z) - z, 0.5f * z);
+  return gate_activation(z, act);
 }
 __device__ __forceinline__ float gated(float g, float u, int act) { return gate_activation(g, act) * u; }
 

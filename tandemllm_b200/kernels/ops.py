@@ -18,7 +18,7 @@ FP32, BF16 = 0, 1
 TL_BAD_ARGUMENT = 100001
 # the gate activations of gated products (TL_ACT_* of csrc/common.cuh) and the router's scoring functions (TL_SCORE_*
 # of csrc/route.cuh), by the names a part's spec gives them
-ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4}
+ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5}
 SCORINGS = {"sigmoid": 0, "softmax": 1}
 
 
@@ -67,7 +67,14 @@ _SIGNATURES = {
     "tl_short_conv_state": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "tl_qk_prepare": [c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                       c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                      c_void_p, c_void_p],
+                      c_int, c_void_p, c_void_p],
+    "tl_add_dyt": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                   c_int, c_void_p],
+    "tl_activation": [c_void_p, c_void_p, c_longlong, c_int, c_float, c_float, c_int, c_void_p],
+    "tl_headmix_spans": [c_int, c_int, c_int],
+    "tl_attention_headmix": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
+                             c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_void_p, c_void_p],
     "tl_kv_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                     c_int, c_int, c_void_p, c_void_p],
     "tl_paged_attention_simt": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int,
@@ -107,6 +114,8 @@ def core():
             fn = getattr(lib, name)
             fn.argtypes = args
             fn.restype = c_int
+        lib.tl_headmix_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        lib.tl_headmix_scratch_floats.restype = c_longlong
         lib.tl_last_error.restype = ctypes.c_char_p
         lib.tl_cuda_error_string.restype = ctypes.c_char_p
         lib.tl_cuda_error_string.argtypes = [c_int]
@@ -252,6 +261,34 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return gated_mul(gate_up, out, ACTIVATIONS["silu"])
 
 
+def add_dyt(residual: torch.Tensor, delta, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,
+            gather: torch.Tensor | None = None) -> torch.Tensor:
+    """residual += delta (32-bit); out = tanh(alpha * residual) * weight + bias, element by element. `delta` is None, a
+    float32 tensor or a branch output in a deferred form (`PartialSums` is added part by part in order; anything else is
+    made a tensor first). `alpha` is a float32 tensor of one element on the device. With `gather` (int32 row indices)
+    output row i is made from row gather[i] and the residual is left unchanged."""
+    _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight"); _need(bias, torch.float32, "norm bias")
+    _need(alpha, torch.float32, "norm alpha"); _need(out, None, "normed")
+    data, parts, stride = None, 0, 0
+    if isinstance(delta, PartialSums) and delta.dtype is None:
+        data, parts, stride = delta.data, delta.parts, delta.rows * delta.hidden
+    elif delta is not None:
+        data, parts = materialize(delta), 1
+        _need(data, torch.float32, "delta")
+    check(core().tl_add_dyt(ptr(residual), ptr(data), parts, stride, ptr(weight), ptr(bias), ptr(alpha), ptr(out), ptr(gather),
+                            out.shape[0], residual.shape[-1], dtype_code(out.dtype), stream()), "add_dyt")
+    return out
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, act: int, a0: float = 0.0, a1: float = 0.0) -> torch.Tensor:
+    """out = act(x) element by element (may be x itself); `act` a code of ACTIVATIONS, `a0`, `a1` its constants (xielu: the
+    factors of its two branches)."""
+    _need(x, out.dtype, "x"); _need(out, None, "out")
+    check(core().tl_activation(ptr(x), ptr(out), x.numel(), int(act), float(a0), float(a1), dtype_code(out.dtype), stream()),
+          "activation")
+    return out
+
+
 # ------------------------------------------------------------------------------------------ products
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, out: torch.Tensor) -> torch.Tensor:
     """out[M, N] = x[M, K] @ w[N, K]^T (+ bias) on the CUDA cores with 32-bit accumulation."""
@@ -321,8 +358,13 @@ def short_conv_state(bcx, state, state_slot, row_start, positions, requests: int
 
 
 # ------------------------------------------------------------------------------------------ attention
+QK_UNIT_NORM, QK_VALUES_ARE_KEYS = 1, 2      # `flags` of qk_prepare (TL_QK_* of csrc/attention_simt.cu)
+
+
 def qk_prepare(qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions, req_of_row, block_table, page_size,
-               q_out, k_cache, v_cache, k_out, v_out, num_heads, num_kv_heads, head_dim, status) -> None:
+               q_out, k_cache, v_cache, k_out, v_out, num_heads, num_kv_heads, head_dim, status, flags: int = 0) -> None:
+    """`flags`: QK_UNIT_NORM brings q and k to unit root mean square without norm weights; QK_VALUES_ARE_KEYS: the rows
+    hold query and key heads only, and a key as projected (before its norm) is stored as its value."""
     _need(qkv, None, "qkv")
     rows = qkv.shape[0]
     max_pages = block_table.shape[1] if block_table is not None else 0
@@ -330,7 +372,7 @@ def qk_prepare(qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions, re
                                int(rotary_dim), ptr(positions), ptr(req_of_row), ptr(block_table), max_pages,
                                int(page_size), k_cache.shape[0] if k_cache is not None else 0, ptr(q_out), ptr(k_cache),
                                ptr(v_cache), ptr(k_out), ptr(v_out), rows,
-                               num_heads, num_kv_heads, head_dim, dtype_code(qkv.dtype), ptr(status), stream()),
+                               num_heads, num_kv_heads, head_dim, dtype_code(qkv.dtype), int(flags), ptr(status), stream()),
           "qk_prepare")
 
 
@@ -391,6 +433,38 @@ def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int
     check(core().tl_attention_join(ptr(scratch), ptr(positions), int(window or 0), ptr(out), rows, Hq, D, int(n_spans),
                                    int(span_keys), dtype_code(out.dtype), stream()), "attention_join",
           kernels=1 if n_spans > 1 else 0)
+
+
+HEADMIX_SPAN = 512      # keys a span of `attention_headmix` when a step's rows are too few to fill the GPU
+
+
+def attention_headmix(q, k_cache, v_cache, block_table, page_size, req_of_row, positions, scale, window, mix, gate, ld_gate,
+                      out, max_context: int, runtime, status) -> torch.Tensor:
+    """Attention with the heads' weights mixed after the softmax by `mix` (float32 [Hq, Hq] or None) and the output of
+    head h times sigmoid(gate[r * ld_gate + h]) (`gate`: a tensor of the compute dtype whose data begins at the first
+    logit, or None). Few rows and many keys are cut into spans of keys; `runtime.scratch` holds what joins them."""
+    _need(q, k_cache.dtype, "q"); _need(out, q.dtype, "out")
+    rows, Hq, D = q.shape
+    Hk = k_cache.shape[1]
+    if mix is not None:
+        _need(mix, torch.float32, "head mix")
+        if tuple(mix.shape) != (Hq, Hq):
+            raise KernelError(f"head mix of shape {tuple(mix.shape)} for {Hq} heads")
+    reach = min(max_context, window + 31) if window else max_context
+    span = max(reach, 32)
+    if rows * 2 <= 148 * 2 and reach > 2 * HEADMIX_SPAN:
+        span = HEADMIX_SPAN
+    span = -(-span // 32) * 32
+    spans = core().tl_headmix_spans(int(max_context), int(window or 0), span)
+    scratch = None
+    if spans > 1:
+        scratch = runtime.scratch("attention", core().tl_headmix_scratch_floats(rows, Hq, D, spans))
+    check(core().tl_attention_headmix(ptr(q), ptr(k_cache), ptr(v_cache), ptr(block_table), block_table.shape[1],
+                                      int(page_size), k_cache.shape[0], ptr(req_of_row), ptr(positions), float(scale),
+                                      int(window or 0), ptr(mix), ptr(gate), int(ld_gate), ptr(out), ptr(scratch), rows, Hq,
+                                      Hk, D, spans, span, dtype_code(q.dtype), ptr(status), stream()), "attention_headmix",
+          kernels=1 if spans == 1 else 3)
+    return out
 
 
 # ------------------------------------------------------------------------------------------ experts

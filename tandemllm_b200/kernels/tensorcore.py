@@ -257,6 +257,16 @@ class TensorCore:
             return True
         return self.gemm(x, w, bias, out, defer=defer) or True
 
+    def linear_act(self, x, w, act: int, a0: float = 0.0, a1: float = 0.0):
+        """act(x @ w^T) in bfloat16 with the activation in the product's epilogue, or None when no kernel here does it
+        for these operands (the caller then runs the product and the activation one after the other)."""
+        return None
+
+    def attention_headmix(self, q, cache, table, step, scale, window, mix, gate, ld_gate, out, runtime) -> bool:
+        """Attention with the heads' weights mixed after the softmax on the tensor cores; False when no kernel here
+        takes these sizes (the caller then uses the CUDA-core kernel)."""
+        return False
+
     def in_proj_conv(self, x, w_in, b_in, taps, b_taps, state, state_slot, req_of_row, positions, y,
                      write_state: bool = True) -> bool:
         """A short-convolution mixer's in-projection and convolution of a decode step of at most 8 rows (one row a

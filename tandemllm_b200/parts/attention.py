@@ -5,6 +5,14 @@ a position encoding, and an optional sliding window.
   cache at the row's position; s = q k^T * scale over the visible keys; softmax in 32-bit; o = a v;
   query head h reads KV head h // (Hq / Hk); out = out_proj(o)      (engine/models/lfm2_moe/ref.py:153-178)
 
+Options, each a parameter of the spec so that another design can name its own combination:
+  `values`: "projected" (a v matrix of its own) or "keys" (no v matrix: a key as projected, before its norm, is its value);
+  `qk_norm`: a norm kind for q and k per head (`rmsnorm` with weights, `unit_rms` without), or None;
+  `head_mix`: the name of a tensor M [Hq, Hq]: after the softmax the heads' weights are mixed, p'_h = sum_g M[h, g] p_g,
+              and head h applies p'_h to the values of its own KV head;
+  `gate`: the name of a matrix [Hq, hidden]: head h's output is multiplied by sigmoid(gate n)_h before the out projection;
+  `weight_suffix`: what follows a matrix's name in the folder (".weight" by default).
+
 Every size (heads, KV heads, head size), the scale, the window and the names of its tensors are
 parameters. The q, k and v matrices are fused into one product at bind time, as the reference's loader
 does (engine/models/lfm2_moe/load.py:125-135). A site that reads another site's cache computes its own
@@ -40,10 +48,19 @@ class AttentionMixer(Part):
         names = spec["names"]
         self.n = {k: prefix + v for k, v in names.items()}
         qk = spec.get("qk_norm")
-        self.q_norm = make_part("norm", qk, prefix=self.n["q_norm"] + ".", size=self.head_dim) if qk else None
-        self.k_norm = make_part("norm", qk, prefix=self.n["k_norm"] + ".", size=self.head_dim) if qk else None
+        self.q_norm = make_part("norm", qk, prefix=self.n.get("q_norm", "") + ".", size=self.head_dim) if qk else None
+        self.k_norm = make_part("norm", qk, prefix=self.n.get("k_norm", "") + ".", size=self.head_dim) if qk else None
         self.position = make_part("position_encoding", spec["position"], head_dim=self.head_dim)
         self.bias = bool(spec.get("bias", False))
+        self.values = str(spec.get("values", "projected"))
+        if self.values not in ("projected", "keys"):
+            raise ValueError(f"values {self.values!r}: projected or keys")
+        self.suffix = str(spec.get("weight_suffix", ".weight"))
+        self.head_mix_name = prefix + spec["head_mix"] if spec.get("head_mix") else None
+        self.gate_name = prefix + spec["gate"] if spec.get("gate") else None
+        self.qk_flags = (ops.QK_UNIT_NORM if qk and qk.kind == "unit_rms" else 0) | \
+                        (ops.QK_VALUES_ARE_KEYS if self.values == "keys" else 0)
+        self.head_mix = None
 
     @property
     def q_dim(self) -> int:
@@ -54,17 +71,34 @@ class AttentionMixer(Part):
         return self.num_kv_heads * self.head_dim
 
     def weight_specs(self, present=None):
-        H = self.hidden_size
-        out = [TensorSpec(self.n["q"] + ".weight", (self.q_dim, H)), TensorSpec(self.n["k"] + ".weight", (self.kv_dim, H)),
-               TensorSpec(self.n["v"] + ".weight", (self.kv_dim, H)), TensorSpec(self.n["out"] + ".weight", (H, self.q_dim))]
+        H, sfx = self.hidden_size, self.suffix
+        out = [TensorSpec(self.n["q"] + sfx, (self.q_dim, H)), TensorSpec(self.n["k"] + sfx, (self.kv_dim, H))]
+        if self.values == "projected":
+            out.append(TensorSpec(self.n["v"] + sfx, (self.kv_dim, H)))
+        out.append(TensorSpec(self.n["out"] + sfx, (H, self.q_dim)))
+        if self.head_mix_name:
+            out.append(TensorSpec(self.head_mix_name, (self.num_heads, self.num_heads), role="vector", init="mix"))
+        if self.gate_name:
+            out.append(TensorSpec(self.gate_name, (self.num_heads, H)))
         if self.q_norm:
             out += self.q_norm.weight_specs() + self.k_norm.weight_specs()
         return out
 
     def bind(self, read, runtime):
         self.runtime = runtime
-        self.w_qkv = torch.cat([runtime.matrix(read(self.n[x] + ".weight")) for x in ("q", "k", "v")]).contiguous()
-        self.w_out = runtime.matrix(read(self.n["out"] + ".weight"))
+        sfx = self.suffix
+        rows = [runtime.matrix(read(self.n[x] + sfx)) for x in (("q", "k", "v") if self.values == "projected" else ("q", "k"))]
+        self.gate_at = sum(r.shape[0] for r in rows)        # the column of the fused product where the gates' logits begin
+        if self.gate_name:
+            # the gate's rows ride at the end of the fused product, filled up with zero rows to a multiple of 8 so that a
+            # row of the product keeps the 16-byte alignment the vector loads and stores want
+            g = runtime.matrix(read(self.gate_name))
+            pad = -(self.gate_at + g.shape[0]) % 8
+            rows += [g, torch.zeros(pad, g.shape[1], dtype=g.dtype, device=g.device)] if pad else [g]
+        self.w_qkv = torch.cat(rows).contiguous()
+        self.w_out = runtime.matrix(read(self.n["out"] + sfx))
+        if self.head_mix_name:
+            self.head_mix = runtime.vector(read(self.head_mix_name))
         if self.q_norm:
             self.q_norm.bind(read, runtime)
             self.k_norm.bind(read, runtime)
@@ -87,20 +121,28 @@ class AttentionMixer(Part):
         if fused is not None and writes_cache:
             inv_freq, rot = fused
             ops.qk_prepare(qkv, qw, kw, eps, inv_freq, rot, step.positions, step.req_of_row, table, cache.page_size,
-                           q, cache.k, cache.v, None, None, Hq, Hk, D, status)
+                           q, cache.k, cache.v, None, None, Hq, Hk, D, status, self.qk_flags)
         else:
             k = torch.empty(R, Hk, D, dtype=dt, device=dev)
             v = torch.empty(R, Hk, D, dtype=dt, device=dev)
             inv_freq, rot = fused if fused is not None else (None, 0)
             ops.qk_prepare(qkv, qw, kw, eps, inv_freq, rot, step.positions, step.req_of_row, None, 0,
-                           q, None, None, k, v, Hq, Hk, D, status)
+                           q, None, None, k, v, Hq, Hk, D, status, self.qk_flags)
             if fused is None:
                 self.position.apply(q, k, step.positions)
             if writes_cache:
                 ops.kv_store(k, v, step.positions, step.req_of_row, table, cache.page_size, cache.k, cache.v, status)
         o = torch.empty(R, Hq, D, dtype=dt, device=dev)
         fast = self.runtime.attention_kernels
-        if fast is None or not fast.attention(q, cache, table, step, self.scale, self.window, o, self.runtime):
+        if self.head_mix is not None or self.gate_name:
+            # the heads' weights are mixed after the softmax (and the output gated a head): kernels of their own
+            gate = qkv[:, self.gate_at:] if self.gate_name else None
+            if fast is None or not fast.attention_headmix(q, cache, table, step, self.scale, self.window, self.head_mix, gate,
+                                                          qkv.stride(0), o, self.runtime):
+                ops.attention_headmix(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,
+                                      self.scale, self.window, self.head_mix, gate, qkv.stride(0), o, step.max_context,
+                                      self.runtime, status)
+        elif fast is None or not fast.attention(q, cache, table, step, self.scale, self.window, o, self.runtime):
             spans = ops.attention_spans(step.max_context)
             scratch = self.runtime.scratch("attention", ops.attention_scratch_floats(R, Hq, D, spans))
             ops.paged_attention_split(q, cache.k, cache.v, table, cache.page_size, step.req_of_row, step.positions,

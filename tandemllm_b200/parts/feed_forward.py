@@ -57,6 +57,61 @@ class SwiGLU(Part):
         return linear(self.runtime, act, self.w_down, out_dtype=torch.float32, defer=True)
 
 
+@register_part("feed_forward", "dense_act")
+class DenseActivation(Part):
+    """The ungated dense feed-forward: out = down( act(up n) ). `activation` names the function (a name of
+    `ops.ACTIVATIONS`); `xielu` reads its two numbers (p, q) from the tensor `act_params` names and uses
+    softplus(p) z^2 + z / 2 for z > 0 and (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise. The two factors are
+    formed once at bind time, in 32-bit, and travel to the kernels as plain numbers."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
+        super().__init__(spec, prefix, hidden_size)
+        self.inter = int(spec["intermediate_size"])
+        self.activation = str(spec.get("activation", "gelu"))
+        self.act = ops.activation_code(self.activation)
+        self.n = {k: prefix + v for k, v in spec["names"].items()}
+        self.a0 = self.a1 = 0.0
+
+    def weight_specs(self, present=None):
+        H, I = self.hidden_size, self.inter
+        out = [TensorSpec(self.n["up"], (I, H)), TensorSpec(self.n["down"], (H, I))]
+        if self.activation == "xielu":
+            out.append(TensorSpec(self.n["act_params"], (2,), role="vector", init="bias"))
+        return out
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        self.w_up = runtime.matrix(read(self.n["up"]))
+        self.w_down = runtime.matrix(read(self.n["down"]))
+        if self.activation == "xielu":
+            pq = read(self.n["act_params"]).to(torch.float32).cpu()
+            sp = torch.nn.functional.softplus(pq)
+            self.a0, self.a1 = float(sp[0]), float(0.5 + sp[1])
+
+    def forward(self, x, step):
+        tc = self.runtime.tensorcore
+        if tc is not None and x.dtype == torch.bfloat16:
+            act = tc.linear_act(x, self.w_up, self.act, self.a0, self.a1)
+            if act is not None:
+                return linear(self.runtime, act, self.w_down, out_dtype=torch.float32, defer=True)
+        act = linear(self.runtime, x, self.w_up)
+        ops.activation(act, act, self.act, self.a0, self.a1)
+        return linear(self.runtime, act, self.w_down, out_dtype=torch.float32, defer=True)
+
+
+@register_part("feed_forward", "none")
+class NoFeedForward(Part):
+    """A layer without a feed-forward: the mixer's output goes on, unadded, to the next layer's first norm."""
+    graph_safe = True
+
+    def forward(self, x, step):
+        return None
+
+    def forward_from(self, norm, residual, delta, step):
+        return delta
+
+
 @register_part("feed_forward", "sigmoid_topk_experts")
 class SigmoidTopKExperts(Part):
     graph_safe = True

@@ -1,4 +1,4 @@
-"""RMS norm fused with the residual add in front of it.
+"""Norms fused with the residual add in front of them: RMS norm, Dynamic Tanh, and the weightless unit-RMS norm of q and k.
 
   y = x * rsqrt(mean(x^2) + eps);  out = w * y      plain w, not 1 + w  (engine/models/lfm2_moe/ref.py:105-109)
 
@@ -50,3 +50,70 @@ class RMSNorm(Part):
         out32 = torch.empty(rows, self.size, dtype=torch.float32, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, out32, route)
         return out, out32
+
+
+@register_part("norm", "dyt")
+class DynamicTanh(Part):
+    """Dynamic Tanh: out = tanh(alpha * x) * w + b, element by element, alpha one scalar a norm; no mean and no variance
+    are computed. Tensors: `<name>` (w), `<name>.b`, `<name>.alpha`, where `<name>` is the prefix without its last dot.
+    With `optional` in the spec the norm reads its tensors only when the folder holds them (a layer whose feed-forward
+    is absent has no use for the norm in front of it)."""
+    graph_safe = True
+
+    def __init__(self, spec, prefix: str = "", size: int = 0, **_):
+        super().__init__(spec, prefix)
+        self.size = size
+        self.eps = float(spec.get("eps", 0.0))          # carried for the mixers that ask their layer's eps; unused here
+        self.name = prefix[:-1] if prefix.endswith(".") else prefix
+        self.optional = bool(spec.get("optional", False))
+        self.weight = self.bias = self.alpha = None
+
+    def weight_specs(self, present=None):
+        if self.optional and (present is None or self.name not in present):
+            return []
+        return [TensorSpec(self.name, (self.size,), role="vector", init="ones"),
+                TensorSpec(self.name + ".b", (self.size,), role="vector", init="bias"),
+                TensorSpec(self.name + ".alpha", (), role="vector", init="ones")]
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        if self.optional:
+            try:
+                read(self.name)
+            except KeyError:
+                return
+        self.weight = runtime.vector(read(self.name))
+        self.bias = runtime.vector(read(self.name + ".b"))
+        self.alpha = runtime.vector(read(self.name + ".alpha")).reshape(1)
+
+    def add_norm(self, residual: torch.Tensor, delta, out: torch.Tensor | None = None,
+                 gather: torch.Tensor | None = None, n_out: int | None = None, want32: bool = False,
+                 route: dict | None = None):
+        if route is not None:
+            raise NotImplementedError("a router inside the Dynamic Tanh kernel")
+        rows = residual.shape[0] if gather is None else (n_out if n_out is not None else gather.shape[0])
+        if out is None:
+            out = torch.empty(rows, self.size, dtype=self.runtime.dtype, device=residual.device)
+        g = gather[:rows] if gather is not None else None
+        ops.add_dyt(residual, delta, self.weight, self.bias, self.alpha, out, g)
+        if not want32:
+            return out
+        if out.dtype == torch.float32:
+            return out, out
+        out32 = torch.empty(rows, self.size, dtype=torch.float32, device=residual.device)
+        # the residual already holds the sum (or, with `gather`, the delta is added once more from its source)
+        ops.add_dyt(residual, delta if gather is not None else None, self.weight, self.bias, self.alpha, out32, g)
+        return out, out32
+
+
+@register_part("norm", "unit_rms")
+class UnitRMS(Part):
+    """x / sqrt(mean(x^2) + eps) without a weight: what a mixer names for q and k that are only brought to unit root
+    mean square. It has no tensors; the mixer's q/k kernel does the arithmetic."""
+    graph_safe = True
+    weight = None
+
+    def __init__(self, spec, prefix: str = "", size: int = 0, **_):
+        super().__init__(spec, prefix)
+        self.size = size
+        self.eps = float(spec["eps"])

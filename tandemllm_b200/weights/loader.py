@@ -28,7 +28,7 @@ class TensorSpec:
     role   "matrix" (multiplied; cast to the compute dtype), "vector" (kept in 32-bit) or "table"
            (integers, int32)
     init   how the random-weights mode fills it: "normal" (N(0, std)), "ones" (1 + N(0, norm_std)),
-           "bias" (N(0, bias_std)) or "zeros"
+           "bias" (N(0, bias_std)), "mix" (the identity + N(0, bias_std)) or "zeros"
     """
     name: str
     shape: tuple[int, ...]

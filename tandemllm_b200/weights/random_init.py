@@ -40,6 +40,8 @@ def random_tensor(spec: TensorSpec, seed: int, std: float, bias_std: float, norm
     t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.init == "ones":
         return 1.0 + norm_std * t if norm_std else torch.ones(spec.shape, dtype=torch.float32, device=device)
+    if spec.init == "mix":          # a square matrix near the identity (a mixing of heads that starts as none)
+        return torch.eye(spec.shape[0], dtype=torch.float32, device=device) + bias_std * t
     return t * (bias_std if spec.init == "bias" else std)
 
 
