@@ -41,7 +41,10 @@ class AttentionMixer(Part):
         self.head_dim = int(spec["head_dim"])
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} query heads are not a multiple of {self.num_kv_heads} KV heads")
-        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+        if spec.get("head_mix") or spec.get("gate"):
+            if not 1 <= self.head_dim <= 256:       # the head-mixing kernels take any head size the q/k kernel does
+                raise ValueError(f"head size {self.head_dim}: 1 to 256 are implemented")
+        elif self.head_dim % 16 or not 16 <= self.head_dim <= 256:
             raise ValueError(f"head size {self.head_dim}: multiples of 16 from 16 to 256 are implemented")
         self.scale = float(spec.get("scale") or self.head_dim ** -0.5)
         self.window = spec.get("window")
