@@ -18,6 +18,10 @@ requests at a context of 8192 tokens. A "step" is one decode step of the whole b
   points     decoded tokens a second at batch 1 and 64 with their roofline fractions, and the headline batch without
              CUDA graphs
 
+`--design sifupel` measures the Sifupel design beside the closest existing model (an LFM2 configuration of attention layers
+and dense feed-forwards only) at a few equal layer sizes: prefill and decode throughput, and every launch summed by kernel
+family with its fraction of the measured peak (its own line; the default workload and line are untouched).
+
 Other modes: `--scenario mixed` (long-context serving through the scheduler, its own line; `--log FILE` writes the
 engine's per-step records as JSON lines), `--profile-table` (one eager decode step and one prefill with every kernel
 launch timed by CUDA events, summed by kernel family: milliseconds, the bytes or flops the family has to move or do,
@@ -354,6 +358,8 @@ class LaunchTimer:
                 "tl_moe_plan": "routing plan", "tl_gather_rows": "rows into expert order", "tl_short_conv": "short conv",
                 "tl_short_conv_decode": "short conv", "tl_short_conv_state": "short conv", "tl_embed_rows": "embedding",
                 "tl_gemm_simt": "32-bit products", "tl_gemm_simt_grouped": "32-bit expert products",
+                "tl_add_dyt": "residual add + norm (Dynamic Tanh)", "tl_activation": "activation",
+                "tl_attention_headmix": "attention", "tl_attention_headmix_mma": "attention",
                 "tl_gated_mul": "gate activation", "tl_argmax": "argmax", "tl_sample": "sampling",
                 "tl_router_topk": "router top-k", "tl_moe_combine": "expert combine", "tl_kv_store": "cache write"}.get(name, name)
 
@@ -445,6 +451,146 @@ def mixed_serving(cfg, model_name: str, a) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------------------ a design beside its neighbour
+DESIGN_SIZES = {
+    "1k": dict(width=1024, layers=8, heads=16, kv=4, dim=64, window=512, ff=4096, vocab=32768),
+    "2k": dict(width=2048, layers=12, heads=32, kv=8, dim=64, window=1024, ff=8192, vocab=65536),
+    "2k-d128": dict(width=2048, layers=12, heads=16, kv=4, dim=128, window=4096, ff=8192, vocab=65536),
+}
+
+
+def design_compare(a) -> int:
+    """Sifupel beside an LFM2 model of attention layers and dense SwiGLU feed-forwards at equal width, depth, heads, head
+    size, vocabulary and feed-forward weight count (SwiGLU's three matrices of 2/3 the width), random weights. For each:
+    a prompt of `--prefill-tokens` tokens, decode steps of `--batch` requests at a context of the window's length (device-
+    timed, from CUDA graphs), and one eager decode step and one prefill with every launch timed, summed by kernel family.
+    Attention's work is counted as visible (row, key) pairs x heads x head size x 4 flops (both products) and, for decode,
+    as the bytes of the visible keys and values; Sifupel's mixing of the heads adds pairs x heads^2 x 2 flops on top."""
+    import torch
+
+    from tandemllm_b200.config import Lfm2MoeConfig, SifupelConfig
+    from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.sampling import SamplingParams
+    pk = peaks()
+    tokens, batch = a.prefill_tokens, a.batch
+    elem = 2 if a.dtype == "bfloat16" else 4
+    out = []
+    for label in (a.design_sizes.split(",") if a.design_sizes else DESIGN_SIZES):
+        z = DESIGN_SIZES[label]
+        W, L, H, G, D, win, ff, V = (z[k] for k in ("width", "layers", "heads", "kv", "dim", "window", "ff", "vocab"))
+        context = win
+        sif = SifupelConfig.from_dict({
+            "architecture": "Sifupel", "vocab": V, "width": W, "norm": {"eps": 1e-5},
+            "layers": [{"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                        "mixer": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": win}}}] * L})
+        inter = (2 * ff // 3 + 255) // 256 * 256
+        lfm = Lfm2MoeConfig.from_dict(dict(CONFIG_8B, vocab_size=V, hidden_size=W, intermediate_size=inter,
+                                           num_hidden_layers=L, num_attention_heads=H, num_key_value_heads=G, head_dim=D,
+                                           num_dense_layers=L, layer_types=["full_attention"] * L))
+        row = {"sizes": dict(z, label=label), "prefill_tokens": tokens, "batch": batch, "context": context}
+        for name, cfg in (("sifupel", sif), ("lfm2_attention_dense", lfm)):
+            room = max(context, tokens) + 4 * a.steps + 64
+            engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
+                dtype=a.dtype, max_len=room, parallel=batch, block_size=16, max_batched_tokens=max(tokens, batch),
+                chunk_size=tokens, graph=a.graph == "on"))
+            for sc in engine.cache.site_cache:
+                sc.k.normal_(0, 0.5)
+                sc.v.normal_(0, 0.5)
+            g = torch.Generator().manual_seed(1)
+            fn = engine.step_function
+            windowed = name == "sifupel"
+
+            def prefill_once(timer=None):
+                engine.admit("prefill")
+                prompt = torch.randint(0, V, (tokens,), generator=g).tolist()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([StepEntry("prefill", prompt, [tokens - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.release("prefill")
+                return e0.elapsed_time(e1)
+            prefill_once()
+            pre_ms = statistics.median(prefill_once() for _ in range(3))
+            timer = LaunchTimer()
+            with timer:
+                prefill_once()
+                pre_table = timer.table()
+            greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+            reqs = [start_with_context(engine, torch.randint(0, V, (context,), generator=g).tolist(),
+                                       SamplingParams(**vars(greedy))) for _ in range(batch)]
+            fn.check_status = False
+            toks = torch.randint(0, V, (3 * a.steps + a.warmup + 4, batch), generator=g).tolist()
+            picked = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+            def one(i):
+                ops.argmax(fn.run([StepEntry(r.request_id, [toks[i][j]], [0]) for j, r in enumerate(reqs)]), picked)
+            for i in range(a.warmup):
+                one(i)
+            torch.cuda.synchronize()
+            regions = []
+            for rep in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(a.warmup + rep * a.steps, a.warmup + (rep + 1) * a.steps):
+                    one(i)
+                e1.record()
+                torch.cuda.synchronize()
+                regions.append(e0.elapsed_time(e1) / a.steps)
+            dec_ms = statistics.median(regions)
+            kept, fn.use_graphs = fn.use_graphs, False
+            one(3 * a.steps + a.warmup)
+            with timer:
+                one(3 * a.steps + a.warmup + 1)
+                dec_table = timer.table()
+            fn.use_graphs = kept
+            fn.check_status = True
+            fn.raise_on_fault()
+            # ---- what each family has to do ----
+            pairs = sum(min(i + 1, win) if windowed else i + 1 for i in range(tokens))
+            att_flops = 4.0 * pairs * H * D * L + (2.0 * pairs * H * H * L if windowed else 0.0)
+            proj = W * (H * D + G * D + (H if windowed else G * D)) + H * D * W
+            ffw = 2 * W * ff if windowed else 3 * W * inter
+            dense_flops = 2.0 * tokens * L * (proj + ffw) + 2.0 * W * V
+            dense_bytes = elem * (L * (proj + ffw) + W * V)
+            kv_bytes = elem * 2.0 * batch * min(context, win if windowed else context) * G * D * L
+
+            def tidy(table, work: dict, unit: str, peak: float, scale: float) -> dict:
+                sums = {}
+                for fam, r in table.items():
+                    key = "attention" if fam.startswith("attention") else "dense products" if fam.startswith(
+                        ("dense", "32-bit products")) else None
+                    if key:
+                        sums[key] = sums.get(key, 0.0) + r["ms"]
+                    r["ms"] = round(r["ms"], 4)
+                for key, ms in sums.items():
+                    rate = work[key] / ms / scale
+                    table[f"= {key}"] = {"ms": round(ms, 4), unit: round(rate, 1), "frac_of_measured_peak": round(rate / peak, 4)}
+                return table
+            row[name] = {
+                "prefill": {"ms": round(pre_ms, 3), "tok_s": round(tokens / pre_ms * 1e3, 1),
+                            "families": tidy(pre_table, {"attention": att_flops, "dense products": dense_flops}, "TFLOPs",
+                                             pk["bf16_tflops"], 1e9)},
+                "decode": {"ms_per_step": round(dec_ms, 4), "tok_s": round(batch / dec_ms * 1e3, 1),
+                           "bytes_per_step": dense_bytes + kv_bytes,
+                           "frac_hbm": round((dense_bytes + kv_bytes) / dec_ms / 1e6 / pk["hbm_gbs"], 4),
+                           "families": tidy(dec_table, {"attention": kv_bytes, "dense products": dense_bytes}, "GBps",
+                                            pk["hbm_gbs"], 1e6)},
+            }
+            for r in reqs:
+                r.num_computed = engine.cache.length_of(r.request_id)
+                engine.scheduler.abort(r)
+            del engine, fn, reqs
+            torch.cuda.empty_cache()
+        out.append(row)
+    print(json.dumps({"design_compare": "sifupel beside lfm2 (attention + dense layers only)", "dtype": a.dtype, "peaks": pk,
+                      "data": "synthetic: random weights, uniform random token ids, random keys and values as context",
+                      "rows": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -479,9 +625,15 @@ def main() -> int:
                     help="programmatic dependent launch between the kernels (for comparison; ordinary launches by default)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--design", choices=("sifupel",),
+                    help="measure this design beside the closest existing model at equal layer sizes (its own line)")
+    ap.add_argument("--design-sizes", default="", help="--design: which of " + ", ".join(DESIGN_SIZES) + " (default: all)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
+    if a.design:
+        a.warmup = max(a.warmup, 3)
+        return design_compare(a)
     if a.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {a.gpus} is not implemented", "n_gpus": a.gpus}))
         return 2

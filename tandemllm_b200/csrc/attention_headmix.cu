@@ -40,13 +40,31 @@ struct HeadMixParams {
   int* status;
 };
 
-__host__ __device__ inline size_t headmix_smem_floats(int Hq, int D) {
-  return (size_t)2 * Hq * D + (size_t)2 * Hq * HM_TILE + (size_t)Hq * Hq + 2 * (size_t)Hq;
+// Shared memory of a block: the row's queries and outputs in 32-bit, two tiles of weights, the mix, the heads' maxima
+// and sums, and the tile's keys and values of `kc` KV heads at a time in the cache's own type (rows padded by 16 bytes,
+// so that a warp's lanes, a key each, read their rows without meeting in a bank).
+template <typename T> __host__ __device__ inline int headmix_row_pad(int D) {
+  return D % (16 / (int)sizeof(T)) == 0 ? D + 16 / (int)sizeof(T) : D + 1;
+}
+template <typename T> __host__ __device__ inline size_t headmix_smem_bytes(int Hq, int D, int kc) {
+  const size_t floats = (size_t)2 * Hq * D + (size_t)2 * Hq * HM_TILE + (size_t)Hq * Hq + 2 * (size_t)Hq;
+  return ((floats * 4 + 15) / 16) * 16 + (size_t)2 * kc * HM_TILE * headmix_row_pad<T>(D) * sizeof(T);
+}
+
+__device__ __forceinline__ void hm_cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;          // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+               "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void hm_cp_async_wait() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 // PHASE 0: both passes (one span). 1: the span's maximum and sum. 2: the joined statistics, then the span's outputs.
+// `kc`: KV heads whose keys and values a block holds in shared memory at a time (all of them where they fit).
 template <typename T, int PHASE>
-__global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixParams p) {
+__global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixParams p, int kc) {
   extern __shared__ __align__(16) float hm_smem[];
   const int Hq = p.Hq, Hk = p.Hk, D = p.D, group = Hq / Hk;
   float* qs = hm_smem;                         // [Hq, D]
@@ -56,6 +74,10 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
   float* mixs = PM + Hq * HM_TILE;             // [Hq, Hq]: M[h, g] / sum_g
   float* ms = mixs + Hq * Hq;                  // [Hq]
   float* ls = ms + Hq;                         // [Hq]
+  const int DP = headmix_row_pad<T>(D);
+  const size_t head_bytes = ((((size_t)2 * Hq * D + (size_t)2 * Hq * HM_TILE + (size_t)Hq * Hq + 2 * (size_t)Hq) * 4 + 15) / 16) * 16;
+  T* sK = reinterpret_cast<T*>(reinterpret_cast<char*>(hm_smem) + head_bytes);      // [kc, 32, DP]
+  T* sV = sK + (size_t)kc * HM_TILE * DP;
   __shared__ long long rowoff[HM_TILE];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = HM_THREADS / 32;
   const int r = blockIdx.x, span = blockIdx.y;
@@ -67,8 +89,6 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
   const int lo = max(first, tile0 + span * p.span_keys);       // this block's keys: lo .. hi
   const int hi = min(pos, tile0 + (span + 1) * p.span_keys - 1);
   const T* Q = (const T*)p.q + (long long)r * Hq * D;
-  const T* K = (const T*)p.k_cache;
-  const T* V = (const T*)p.v_cache;
   // a row whose keys reach past the spans the launch was given: recorded, and the keys beyond are not read
   if (tid == 0 && span == 0 && pos - tile0 >= p.spans * p.span_keys) atomicExch(p.status, 6);
   for (int i = tid; i < Hq * D; i += HM_THREADS) {
@@ -83,6 +103,9 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec_ok = D % VEC == 0;
   const long long head_stride = (long long)p.page_size * D;
+  // heads a unit of work takes together against one key (they share the key's row): as many as keep every warp busy
+  const int hb = max(1, min(min(8, group), (Hq + nwarps - 1) / nwarps));
+  const int blocks_per_group = (group + hb - 1) / hb;
 
   // where the tile's keys lie (KV head 0; -1: not visible from this block, or no page)
   auto locate = [&](int j0) {
@@ -97,44 +120,94 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
       rowoff[tid] = off;
     }
   };
-  // the score of head g against the key of this lane
-  auto score = [&](int g) -> float {
-    const long long off = rowoff[lane];
-    if (off < 0) return -INFINITY;
-    const T* krow = K + off + (long long)(g / group) * head_stride;
-    const float* qg = qs + (size_t)g * D;
-    float acc = 0.f;
+  // the tile's rows of KV heads c0 .. c0 + nc - 1 from `cache` into `dst` (rows that are not seen become zeros)
+  auto stage = [&](const T* cache, T* dst, int c0, int nc) {
     if (vec_ok) {
-      for (int d = 0; d < D; d += VEC) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
-        const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc = fmaf(qg[d + i], to_f32(e[i]), acc);
+      const int per_row = D / VEC, n = nc * HM_TILE * per_row;
+      for (int i = tid; i < n; i += HM_THREADS) {
+        const int ch = i % per_row, jj = (i / per_row) % HM_TILE, cc = i / (per_row * HM_TILE);
+        const long long off = rowoff[jj];
+        const T* src = cache + (off < 0 ? 0 : off + (long long)(c0 + cc) * head_stride + ch * VEC);
+        hm_cp_async16(dst + ((size_t)cc * HM_TILE + jj) * DP + ch * VEC, src, off >= 0);
       }
     } else {
-      for (int d = 0; d < D; ++d) acc = fmaf(qg[d], to_f32(krow[d]), acc);
+      const int n = nc * HM_TILE * D;
+      for (int i = tid; i < n; i += HM_THREADS) {
+        const int d = i % D, jj = (i / D) % HM_TILE, cc = i / (D * HM_TILE);
+        const long long off = rowoff[jj];
+        dst[((size_t)cc * HM_TILE + jj) * DP + d] = off < 0 ? from_f32<T>(0.f) : cache[off + (long long)(c0 + cc) * head_stride + d];
+      }
     }
-    return acc * p.scale;
   };
+  // Scores of the heads of KV heads c0 .. c0 + nc - 1 against the staged keys, a key a lane; `use(g, s)` is called by the
+  // whole warp with head g's score of the lane's key (-inf where the key is not seen).
+  auto scores = [&](int c0, int nc, auto&& use) {
+    const bool seen = rowoff[lane] >= 0;
+    for (int u = warp; u < nc * blocks_per_group; u += nwarps) {
+      const int cc = u / blocks_per_group, g0 = (c0 + cc) * group + (u % blocks_per_group) * hb;
+      const int nh = min(hb, (c0 + cc + 1) * group - g0);
+      const T* krow = sK + ((size_t)cc * HM_TILE + lane) * DP;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      if (vec_ok) {
+        for (int d = 0; d < D; d += VEC) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
+          const T* e = reinterpret_cast<const T*>(&raw);
+          float f[VEC];
+#pragma unroll
+          for (int x = 0; x < VEC; ++x) f[x] = to_f32(e[x]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i < nh) {
+              const float* qg = qs + (size_t)(g0 + i) * D + d;
+#pragma unroll
+              for (int x = 0; x < VEC; x += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qg + x);
+                acc[i] = fmaf(q4.x, f[x], acc[i]); acc[i] = fmaf(q4.y, f[x + 1], acc[i]);
+                acc[i] = fmaf(q4.z, f[x + 2], acc[i]); acc[i] = fmaf(q4.w, f[x + 3], acc[i]);
+              }
+            }
+          }
+        }
+      } else {
+        for (int d = 0; d < D; ++d) {
+          const float f = to_f32(krow[d]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (i < nh) acc[i] = fmaf(qs[(size_t)(g0 + i) * D + d], f, acc[i]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < nh) use(g0 + i, seen ? acc[i] * p.scale : -INFINITY);
+    }
+  };
+  const bool whole = kc >= Hk;        // every KV head's tile fits at once: keys and values are staged together
 
   if (PHASE != 2) {
     for (int j0 = lo / HM_TILE * HM_TILE; j0 <= hi; j0 += HM_TILE) {
       locate(j0);
       __syncthreads();
-      for (int g = warp; g < Hq; g += nwarps) {
-        const float s = score(g);
-        const float tmax = warp_max(s);
-        if (tmax == -INFINITY) continue;
-        const float m_old = ms[g], m_new = fmaxf(m_old, tmax);
-        const float sum = warp_sum(s == -INFINITY ? 0.f : expf(s - m_new));
-        __syncwarp();
-        if (lane == 0) {
-          ls[g] = (m_old == -INFINITY ? 0.f : ls[g] * expf(m_old - m_new)) + sum;
-          ms[g] = m_new;
-        }
-        __syncwarp();
+      for (int c0 = 0; c0 < Hk; c0 += kc) {
+        const int nc = min(kc, Hk - c0);
+        stage((const T*)p.k_cache, sK, c0, nc);
+        hm_cp_async_wait();
+        __syncthreads();
+        scores(c0, nc, [&](int g, float s) {
+          const float tmax = warp_max(s);
+          if (tmax == -INFINITY) return;
+          const float m_old = ms[g], m_new = fmaxf(m_old, tmax);
+          const float sum = warp_sum(s == -INFINITY ? 0.f : expf(s - m_new));
+          __syncwarp();
+          if (lane == 0) {
+            ls[g] = (m_old == -INFINITY ? 0.f : ls[g] * expf(m_old - m_new)) + sum;
+            ms[g] = m_new;
+          }
+          __syncwarp();
+        });
+        __syncthreads();
       }
-      __syncthreads();
     }
   }
   if (PHASE == 1) {
@@ -170,11 +243,15 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
   for (int j0 = lo / HM_TILE * HM_TILE; j0 <= hi; j0 += HM_TILE) {
     locate(j0);
     __syncthreads();
-    for (int g = warp; g < Hq; g += nwarps) {
-      const float s = score(g);
-      P[g * HM_TILE + lane] = s == -INFINITY ? 0.f : expf(s - ms[g]);
+    for (int c0 = 0; c0 < Hk; c0 += kc) {
+      const int nc = min(kc, Hk - c0);
+      stage((const T*)p.k_cache, sK, c0, nc);
+      if (whole) stage((const T*)p.v_cache, sV, 0, Hk);
+      hm_cp_async_wait();
+      __syncthreads();
+      scores(c0, nc, [&](int g, float s) { P[g * HM_TILE + lane] = s == -INFINITY ? 0.f : expf(s - ms[g]); });
+      __syncthreads();
     }
-    __syncthreads();
     for (int i = tid; i < Hq * HM_TILE; i += HM_THREADS) {
       const int h = i / HM_TILE, jj = i - h * HM_TILE;
       const float* mh = mixs + h * Hq;
@@ -184,41 +261,48 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
     }
     __syncthreads();
     const int jj_lo = max(lo - j0, 0), jj_hi = min(hi - j0, HM_TILE - 1);
-    if (D % 4 == 0) {
-      for (int o4 = tid; o4 < Hq * D / 4; o4 += HM_THREADS) {
-        const int o = o4 * 4, h = o / D, d = o - h * D;
-        const long long hoff = (long long)(h / group) * head_stride + d;
-        float4 acc = *reinterpret_cast<const float4*>(osm + o);
-        for (int jj = jj_lo; jj <= jj_hi; ++jj) {
-          const long long off = rowoff[jj];
-          if (off < 0) continue;
-          const float w = PM[h * HM_TILE + jj];
-          const T* v = V + off + hoff;
-          if constexpr (sizeof(T) == 4) {
-            const float4 x = *reinterpret_cast<const float4*>(v);
-            acc.x = fmaf(w, x.x, acc.x); acc.y = fmaf(w, x.y, acc.y); acc.z = fmaf(w, x.z, acc.z); acc.w = fmaf(w, x.w, acc.w);
-          } else {
-            const uint2 raw = *reinterpret_cast<const uint2*>(v);
-            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            const float2 a = __bfloat1622float2(h2[0]), c2 = __bfloat1622float2(h2[1]);
-            acc.x = fmaf(w, a.x, acc.x); acc.y = fmaf(w, a.y, acc.y); acc.z = fmaf(w, c2.x, acc.z); acc.w = fmaf(w, c2.y, acc.w);
+    for (int c0 = 0; c0 < Hk; c0 += kc) {
+      const int nc = min(kc, Hk - c0);
+      if (!whole) {
+        stage((const T*)p.v_cache, sV, c0, nc);
+        hm_cp_async_wait();
+        __syncthreads();
+      }
+      const int h_first = c0 * group, n_heads = nc * group;
+      if (vec_ok) {
+        for (int o4 = tid; o4 < n_heads * D / 4; o4 += HM_THREADS) {
+          const int o = h_first * D + o4 * 4, h = o / D, d = o - h * D;
+          const T* vcol = sV + ((size_t)(h / group - c0) * HM_TILE) * DP + d;
+          const float* w = PM + h * HM_TILE;
+          float4 acc = *reinterpret_cast<const float4*>(osm + o);
+#pragma unroll 4
+          for (int jj = jj_lo; jj <= jj_hi; ++jj) {
+            const T* v = vcol + (size_t)jj * DP;
+            if constexpr (sizeof(T) == 4) {
+              const float4 x = *reinterpret_cast<const float4*>(v);
+              acc.x = fmaf(w[jj], x.x, acc.x); acc.y = fmaf(w[jj], x.y, acc.y);
+              acc.z = fmaf(w[jj], x.z, acc.z); acc.w = fmaf(w[jj], x.w, acc.w);
+            } else {
+              const uint2 raw = *reinterpret_cast<const uint2*>(v);
+              const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+              const float2 a = __bfloat1622float2(h2[0]), c2 = __bfloat1622float2(h2[1]);
+              acc.x = fmaf(w[jj], a.x, acc.x); acc.y = fmaf(w[jj], a.y, acc.y);
+              acc.z = fmaf(w[jj], c2.x, acc.z); acc.w = fmaf(w[jj], c2.y, acc.w);
+            }
           }
+          *reinterpret_cast<float4*>(osm + o) = acc;
         }
-        *reinterpret_cast<float4*>(osm + o) = acc;
-      }
-    } else {
-      for (int o = tid; o < Hq * D; o += HM_THREADS) {
-        const int h = o / D, d = o - h * D;
-        const long long hoff = (long long)(h / group) * head_stride + d;
-        float acc = osm[o];
-        for (int jj = jj_lo; jj <= jj_hi; ++jj) {
-          const long long off = rowoff[jj];
-          if (off >= 0) acc = fmaf(PM[h * HM_TILE + jj], to_f32(V[off + hoff]), acc);
+      } else {
+        for (int oi = tid; oi < n_heads * D; oi += HM_THREADS) {
+          const int o = h_first * D + oi, h = o / D, d = o - h * D;
+          const T* vcol = sV + ((size_t)(h / group - c0) * HM_TILE) * DP + d;
+          float acc = osm[o];
+          for (int jj = jj_lo; jj <= jj_hi; ++jj) acc = fmaf(PM[h * HM_TILE + jj], to_f32(vcol[(size_t)jj * DP]), acc);
+          osm[o] = acc;
         }
-        osm[o] = acc;
       }
+      __syncthreads();
     }
-    __syncthreads();
   }
   if (PHASE == 2) {
     float* dst = p.partial + ((long long)r * p.spans + span) * Hq * D;
@@ -250,7 +334,10 @@ __global__ void headmix_join_kernel(HeadMixParams p) {
 
 template <typename T>
 static int headmix_launch(const HeadMixParams& p, cudaStream_t stream) {
-  const size_t smem = headmix_smem_floats(p.Hq, p.D) * sizeof(float);
+  // as many KV heads' tiles at a time as keep a block within 110 KB (two blocks an SM), one at least
+  int kc = p.Hk;
+  while (kc > 1 && headmix_smem_bytes<T>(p.Hq, p.D, kc) > 110 * 1024) kc = (kc + 1) / 2;
+  const size_t smem = headmix_smem_bytes<T>(p.Hq, p.D, kc);
   TL_REQUIRE(smem <= 200 * 1024, "head-mixed attention: %d heads of size %d need %zu bytes of shared memory a block",
              p.Hq, p.D, smem);
   dim3 grid(p.rows, p.spans);
@@ -261,7 +348,7 @@ static int headmix_launch(const HeadMixParams& p, cudaStream_t stream) {
                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
       if (e_ != cudaSuccess) return (int)e_;                                                                           \
     }                                                                                                                  \
-    headmix_attention_kernel<T, PHASE_><<<grid, HM_THREADS, smem, stream>>>(p);                                        \
+    headmix_attention_kernel<T, PHASE_><<<grid, HM_THREADS, smem, stream>>>(p, kc);                                      \
     TL_LAUNCH_CHECK();                                                                                                 \
   } while (0)
   if (p.spans == 1) {

@@ -435,7 +435,17 @@ def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int
           kernels=1 if n_spans > 1 else 0)
 
 
-HEADMIX_SPAN = 512      # keys a span of `attention_headmix` when a step's rows are too few to fill the GPU
+HEADMIX_SPAN = 64       # the fewest keys a span of `attention_headmix` holds (a step's rows too few to fill the GPU)
+
+
+_sm_count = None
+
+
+def sm_count() -> int:
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
 
 
 def attention_headmix(q, k_cache, v_cache, block_table, page_size, req_of_row, positions, scale, window, mix, gate, ld_gate,
@@ -451,9 +461,9 @@ def attention_headmix(q, k_cache, v_cache, block_table, page_size, req_of_row, p
         if tuple(mix.shape) != (Hq, Hq):
             raise KernelError(f"head mix of shape {tuple(mix.shape)} for {Hq} heads")
     reach = min(max_context, window + 31) if window else max_context
-    span = max(reach, 32)
-    if rows * 2 <= 148 * 2 and reach > 2 * HEADMIX_SPAN:
-        span = HEADMIX_SPAN
+    # few rows and many keys: spans of keys, enough of them for two blocks an SM, none shorter than HEADMIX_SPAN
+    wanted = max(1, (2 * sm_count()) // max(rows, 1))
+    span = max(HEADMIX_SPAN, -(-reach // wanted))
     span = -(-span // 32) * 32
     spans = core().tl_headmix_spans(int(max_context), int(window or 0), span)
     scratch = None
