@@ -50,6 +50,7 @@ PROMPT_ATTENTION = "tcgen05"    # prompt portions of head size 64: the tcgen05 k
 PROMPT_PRODUCT = SETTINGS.get("PROMPT_PRODUCT")
 if PROMPT_PRODUCT not in ("pair", "single"):
     raise ValueError(f"TANDEMLLM_PROMPT_PRODUCT={PROMPT_PRODUCT!r}: pair or single")
+HEADMIX_PROMPT_ROWS = 8         # rows a request must bring for a step's head-mixed attention to run on the tensor cores
 PAIR_HALF_ROWS = 64             # rows an expert (on average) up to which the experts' pair products run two CTAs an SM
 _lib = None
 
@@ -91,6 +92,14 @@ def lib():
         l.tl_attention_mma_tile_rows.restype = c_int
         l.tl_attention_mma_supported.argtypes = [c_int, c_int, c_int]
         l.tl_attention_mma_supported.restype = c_int
+        l.tl_attention_headmix_mma_supported.argtypes = [c_int, c_int, c_int]
+        l.tl_attention_headmix_mma_supported.restype = c_int
+        l.tl_attention_headmix_mma_tile_rows.argtypes = []
+        l.tl_attention_headmix_mma_tile_rows.restype = c_int
+        l.tl_attention_headmix_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                                               c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int,
+                                               c_int, c_int, c_void_p, c_void_p]
+        l.tl_attention_headmix_mma.restype = c_int
         l.tl_gemm_skinny_supported.argtypes = [c_int, c_int, c_int, c_longlong, c_longlong]
         l.tl_gemm_skinny_supported.restype = c_int
         l.tl_gemm_skinny_mma.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int,
@@ -263,9 +272,21 @@ class TensorCore:
         return None
 
     def attention_headmix(self, q, cache, table, step, scale, window, mix, gate, ld_gate, out, runtime) -> bool:
-        """Attention with the heads' weights mixed after the softmax on the tensor cores; False when no kernel here
-        takes these sizes (the caller then uses the CUDA-core kernel)."""
-        return False
+        """Attention with the heads' weights mixed after the softmax on the tensor cores (csrc/attention_headmix_mma.cu), for
+        steps that bring prompt portions; False when the kernel does not take the sizes or the step is one of single rows
+        (the caller then uses the CUDA-core kernel, which splits long contexts over blocks)."""
+        R, Hq, D = q.shape
+        Hk = cache.k.shape[1]
+        if (q.dtype != torch.bfloat16 or step.max_rows_per_request < HEADMIX_PROMPT_ROWS
+                or not lib().tl_attention_headmix_mma_supported(Hq, Hk, D)):
+            return False
+        tiles = self.query_tiles(step, lib().tl_attention_headmix_mma_tile_rows())
+        _check(lib().tl_attention_headmix_mma(
+            q.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size,
+            cache.k.shape[0], tiles.data_ptr(), tiles.shape[0], step.positions.data_ptr(), float(scale), int(window or 0),
+            ops.ptr(mix), ops.ptr(gate), int(ld_gate), out.data_ptr(), Hq, Hk, D, self.status.data_ptr(), ops.stream()),
+            "attention_headmix_mma")
+        return True
 
     def in_proj_conv(self, x, w_in, b_in, taps, b_taps, state, state_slot, req_of_row, positions, y,
                      write_state: bool = True) -> bool:

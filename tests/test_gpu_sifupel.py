@@ -387,3 +387,41 @@ def test_the_replay_program_on_a_folder(dtype, tmp_path, plain_logits):
     assert rel(a, wx[[0, 24]]) < TOL[dtype]
     assert rel(b, torch.stack([wx[39], wy[18]])) < TOL[dtype]
     assert not (out / "2.f32").exists()
+
+
+@pytest.mark.parametrize("H,G,D,window,T_", [(8, 2, 64, 40, 150), (4, 1, 64, 0, 100), (16, 4, 64, 70, 120), (32, 8, 64, 33, 90),
+                                               (12, 4, 128, 50, 130), (3, 3, 128, 1, 40)])
+def test_head_mixed_attention_on_the_tensor_cores(H, G, D, window, T_):
+    """The prompt kernel of the bfloat16 path at its own entry point: tiles of 16 rows and a last, shorter one, a second
+    request that begins in the middle of a page's worth of rows, every number of heads a warp (1, 2, 4), windows' edges
+    inside and across key tiles, on shuffled pages."""
+    from tandemllm_b200.kernels import tensorcore
+    from tandemllm_b200.parts.base import Runtime
+    lib = tensorcore.lib()
+    assert lib.tl_attention_headmix_mma_supported(H, G, D)
+    dt, dev = torch.bfloat16, torch.device("cuda")
+    rt = Runtime(dev, dt)
+    g = torch.Generator().manual_seed(H + D + T_)
+    q = torch.randn(T_, H, D, generator=g).to(dt)
+    k = torch.randn(T_, G, D, generator=g).to(dt)
+    v = torch.randn(T_, G, D, generator=g).to(dt)
+    mix = torch.eye(H) + 0.4 * torch.randn(H, H, generator=g)
+    gate = torch.randn(T_, H + 5, generator=g).to(dt)
+    want = _plain_headmix(q.float(), k.float(), v.float(), 0.23, window, mix, gate[:, :H].float())
+    kc, vc, table = _paged(k, v, 16, seed=T_ + 1)
+    # the step brings the sequence's last rows only (the earlier keys are in the cache), cut into tiles of 16 rows
+    first = 37
+    rows = T_ - first
+    tiles = torch.tensor([(0, r0, min(16, rows - r0)) for r0 in range(0, rows, 16)], dtype=torch.int32, device=dev)
+    out = torch.zeros(rows, H, D, dtype=dt, device=dev)
+    gd = gate[first:].contiguous().to(dev)
+    qd, kd, vd, td, md = q[first:].contiguous().to(dev), kc.to(dev), vc.to(dev), table.to(dev), mix.to(dev)
+    pos = torch.arange(first, T_, dtype=torch.int32, device=dev)
+    code = lib.tl_attention_headmix_mma(
+        qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), td.data_ptr(), td.shape[1], 16, kd.shape[0], tiles.data_ptr(),
+        tiles.shape[0], pos.data_ptr(), 0.23, window, md.data_ptr(), gd.data_ptr(), gd.stride(0), out.data_ptr(), H, G, D,
+        rt.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert code == 0
+    torch.cuda.synchronize()
+    assert int(rt.status.item()) == 0
+    assert rel(out.float().view(rows, -1), want[first:].reshape(rows, -1)) < 2e-2
