@@ -28,10 +28,9 @@ __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
   const int bytes = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(saddr(dst)), "l"(src), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void cp_wait_all() {
-  asm volatile("cp.async.commit_group;" ::: "memory");
-  asm volatile("cp.async.wait_group 0;" ::: "memory");
-}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's committed groups are still in flight (the most recent ones)
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -65,7 +64,8 @@ struct Params {
 };
 
 template <int D> __host__ __device__ inline size_t smem_bytes(int Hq, int Hk) {
-  return (size_t)Hq * BM * D * 2 + (size_t)2 * Hk * TJ * D * 2 + (size_t)Hq * BM * PS * 4 + (size_t)Hq * Hq * 4;
+  const size_t hq_max = (size_t)(Hq + 7) / 8 * 8 <= 8 ? 8 : ((Hq + 7) / 8 <= 2 ? 16 : 32);     // 8 x heads a warp
+  return (size_t)Hq * BM * D * 2 + (size_t)2 * Hk * TJ * D * 2 + (size_t)Hq * BM * PS * 4 + hq_max * hq_max * 4;
 }
 
 template <int D, int HPW>
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
   uint8_t* sK = sQ + (size_t)Hq * BM * D * 2;                   // [Hk][32][D]
   uint8_t* sV = sK + (size_t)Hk * TJ * D * 2;                   // [Hk][32][D]
   float* sP = reinterpret_cast<float*>(sV + (size_t)Hk * TJ * D * 2);      // [Hq][16][PS]
-  float* sM = sP + (size_t)Hq * BM * PS;                        // [Hq][Hq]
+  float* sM = sP + (size_t)Hq * BM * PS;                        // [HQMAX][HQMAX], zeros beyond the model's heads
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int t = blockIdx.x;
   const int b = p.tiles[3 * t], row0 = p.tiles[3 * t + 1], nq = min(p.tiles[3 * t + 2], BM);
@@ -93,30 +93,41 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
     const bool valid = m < nq;
     cp16(sQ + (size_t)g * BM * D * 2 + swz<D>(m, c), p.q + ((long long)(row0 + (valid ? m : 0)) * Hq + g) * D + c * 8, valid);
   }
-  for (int i = tid; i < Hq * Hq; i += THREADS) sM[i] = p.mix ? p.mix[i] : ((i / Hq) == (i % Hq) ? 1.f : 0.f);
+  for (int i = tid; i < HQMAX * HQMAX; i += THREADS) {
+    const int h = i / HQMAX, g = i % HQMAX;
+    sM[i] = (h < Hq && g < Hq) ? (p.mix ? p.mix[h * Hq + g] : (h == g ? 1.f : 0.f)) : 0.f;
+  }
 
+  // A thread copies the same 16-byte chunk of the same key for every KV head: the key's page is looked up once a tile.
+  static_assert(THREADS % CH == 0 && (TJ * CH) % THREADS == 0, "whole keys a round of the block's threads");
+  const long long kv_head_stride = (long long)p.page_size * D;
   auto stage = [&](const bf16* cache, uint8_t* dst, int j0) {
-    for (int i = tid; i < Hk * TJ * CH; i += THREADS) {
-      const int c = i % CH, jj = (i / CH) % TJ, cc = i / (CH * TJ);
+    const int c = tid % CH;
+#pragma unroll
+    for (int rnd = 0; rnd < TJ * CH / THREADS; ++rnd) {
+      const int jj = tid / CH + rnd * (THREADS / CH);
       const int kp = j0 + jj;
       bool valid = kp >= k_lo && kp <= k_hi;
       long long off = 0;
       if (valid) {
-        const int page = table_page(table, kp / p.page_size, p.max_pages, p.num_pages);
+        const int pg = kp / p.page_size;
+        const int page = table_page(table, pg, p.max_pages, p.num_pages);
         if (page < 0) {
           atomicExch(p.status, 3);
           valid = false;
         } else {
-          off = (((long long)page * Hk + cc) * p.page_size + kp % p.page_size) * D + c * 8;
+          off = ((long long)page * Hk * p.page_size + (kp - pg * p.page_size)) * D + c * 8;
         }
       }
-      cp16(dst + (size_t)cc * TJ * D * 2 + swz<D>(jj, c), cache + off, valid);
+      uint8_t* to = dst + swz<D>(jj, c);
+      const bf16* from = cache + off;
+      for (int cc = 0; cc < Hk; ++cc) cp16(to + (size_t)cc * TJ * D * 2, valid ? from + cc * kv_head_stride : cache, valid);
     }
   };
   // S = Q_g K_c^T for the tile: s[n][0..1] row lane / 4, keys 8 n + 2 (lane % 4) + {0, 1}; s[n][2..3] row lane / 4 + 8
-  auto qk = [&](int g, float (*s)[4]) {
+  auto qk = [&](int g, const uint8_t* keys, float (*s)[4]) {
     const uint8_t* q_tile = sQ + (size_t)g * BM * D * 2;
-    const uint8_t* k_tile = sK + (size_t)(g / group) * TJ * D * 2;
+    const uint8_t* k_tile = keys + (size_t)(g / group) * TJ * D * 2;
 #pragma unroll
     for (int n = 0; n < 4; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
 #pragma unroll
@@ -159,16 +170,27 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
   const int j_first = k_lo / TJ * TJ;
 
   // ---- pass 1: every head's maximum and sum a row ----
-  for (int j0 = j_first; j0 <= k_hi; j0 += TJ) {
-    stage(p.k_cache, sK, j0);
-    cp_wait_all();
+  // (the values' tile is not needed yet: it serves as a second tile of keys, so that a tile loads while the one before
+  // it is worked on)
+  stage(p.k_cache, sK, j_first);
+  cp_commit();
+  int cur = 0;
+  for (int j0 = j_first; j0 <= k_hi; j0 += TJ, cur ^= 1) {
+    if (j0 + TJ <= k_hi) {
+      stage(p.k_cache, cur ? sK : sV, j0 + TJ);
+      cp_commit();
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
     __syncthreads();
+    const uint8_t* keys = cur ? sV : sK;
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
       const int g = warp + 8 * i;
       if (g < Hq) {
         float s[4][4];
-        qk(g, s);
+        qk(g, keys, s);
         mask_scale(s, j0);
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -186,8 +208,8 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
-          sum0 += expf(s[n][0] - c0) + expf(s[n][1] - c0);
-          sum1 += expf(s[n][2] - c1) + expf(s[n][3] - c1);
+          sum0 += __expf(s[n][0] - c0) + __expf(s[n][1] - c0);
+          sum1 += __expf(s[n][2] - c1) + __expf(s[n][3] - c1);
         }
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
         sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
@@ -216,50 +238,69 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
     for (int n = 0; n < D / 8; ++n) o[i][n][0] = o[i][n][1] = o[i][n][2] = o[i][n][3] = 0.f;
 
   // ---- pass 2: the weights, mixed over the heads, applied to the values ----
+  // The next tile's keys load while this tile's weights are mixed and applied, the next tile's values while the next
+  // scores are formed: a thread's copies complete in the order of their groups, keys (j), values (j), keys (j + 1), ...
+  stage(p.k_cache, sK, j_first);
+  cp_commit();
+  stage(p.v_cache, sV, j_first);
+  cp_commit();
   for (int j0 = j_first; j0 <= k_hi; j0 += TJ) {
-    stage(p.k_cache, sK, j0);
-    stage(p.v_cache, sV, j0);
-    cp_wait_all();
+    const bool more = j0 + TJ <= k_hi;
+    cp_wait<1>();                       // this tile's keys
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
       const int g = warp + 8 * i;
       if (g < Hq) {
         float s[4][4];
-        qk(g, s);
+        qk(g, sK, s);
         mask_scale(s, j0);
         float* pg = sP + (size_t)g * BM * PS;
 #pragma unroll
         for (int n = 0; n < 4; ++n) {
           const int col = n * 8 + (lane & 3) * 2;
           *reinterpret_cast<float2*>(pg + r_lo * PS + col) =
-              make_float2(expf(s[n][0] - m_run[i][0]) * l_run[i][0], expf(s[n][1] - m_run[i][0]) * l_run[i][0]);
+              make_float2(__expf(s[n][0] - m_run[i][0]) * l_run[i][0], __expf(s[n][1] - m_run[i][0]) * l_run[i][0]);
           *reinterpret_cast<float2*>(pg + r_hi * PS + col) =
-              make_float2(expf(s[n][2] - m_run[i][1]) * l_run[i][1], expf(s[n][3] - m_run[i][1]) * l_run[i][1]);
+              make_float2(__expf(s[n][2] - m_run[i][1]) * l_run[i][1], __expf(s[n][3] - m_run[i][1]) * l_run[i][1]);
         }
       }
     }
     __syncthreads();
-    if (p.mix) {
-      // a thread owns (row, key) places and mixes all heads there: p'_h = sum_g M[h, g] p_g, in place
-#pragma unroll
-      for (int rep = 0; rep < BM * TJ / THREADS; ++rep) {
-        const int idx = tid + rep * THREADS, mi = idx / TJ, mj = idx % TJ;
-        float* at = sP + mi * PS + mj;
-        float pv[HQMAX];
-#pragma unroll
-        for (int g = 0; g < HQMAX; ++g) pv[g] = g < Hq ? at[(size_t)g * BM * PS] : 0.f;
-        for (int h = 0; h < Hq; ++h) {
-          const float* mh = sM + h * Hq;
-          float acc = 0.f;
-#pragma unroll
-          for (int g = 0; g < HQMAX; ++g)
-            if (g < Hq) acc = fmaf(mh[g], pv[g], acc);
-          at[(size_t)h * BM * PS] = acc;
-        }
-      }
-      __syncthreads();
+    if (more) {
+      stage(p.k_cache, sK, j0 + TJ);
+      cp_commit();
     }
+    if (p.mix) {
+      // a thread owns two (row, key) places and mixes all heads there: p'_h = sum_g M[h, g] p_g, in place. The mix's
+      // rows are read 16 bytes at a time (the same address for every thread), each value used for both places.
+      static_assert(BM * TJ == 2 * THREADS, "two places a thread");
+      float* at0 = sP + (tid / TJ) * PS + tid % TJ;
+      float* at1 = at0 + (THREADS / TJ) * PS;
+      float pa[HQMAX], pb[HQMAX];
+#pragma unroll
+      for (int g = 0; g < HQMAX; ++g) {
+        pa[g] = g < Hq ? at0[(size_t)g * BM * PS] : 0.f;
+        pb[g] = g < Hq ? at1[(size_t)g * BM * PS] : 0.f;
+      }
+      for (int h = 0; h < Hq; ++h) {
+        const float4* mh = reinterpret_cast<const float4*>(sM + h * HQMAX);
+        float acc_a = 0.f, acc_b = 0.f;
+#pragma unroll
+        for (int g4 = 0; g4 < HQMAX / 4; ++g4) {
+          const float4 m4 = mh[g4];
+          acc_a = fmaf(m4.x, pa[4 * g4], acc_a); acc_b = fmaf(m4.x, pb[4 * g4], acc_b);
+          acc_a = fmaf(m4.y, pa[4 * g4 + 1], acc_a); acc_b = fmaf(m4.y, pb[4 * g4 + 1], acc_b);
+          acc_a = fmaf(m4.z, pa[4 * g4 + 2], acc_a); acc_b = fmaf(m4.z, pb[4 * g4 + 2], acc_b);
+          acc_a = fmaf(m4.w, pa[4 * g4 + 3], acc_a); acc_b = fmaf(m4.w, pb[4 * g4 + 3], acc_b);
+        }
+        at0[(size_t)h * BM * PS] = acc_a;
+        at1[(size_t)h * BM * PS] = acc_b;
+      }
+    }
+    if (more) cp_wait<1>();             // this tile's values (the next tile's keys may still be on their way)
+    else cp_wait<0>();
+    __syncthreads();
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
       const int h = warp + 8 * i;
@@ -286,6 +327,10 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
       }
     }
     __syncthreads();
+    if (more) {
+      stage(p.v_cache, sV, j0 + TJ);
+      cp_commit();
+    }
   }
 
   // ---- gate and store ----
