@@ -319,17 +319,25 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
 
 // out = gate * (the spans' partial outputs added in span order)
 template <typename T>
-__global__ void headmix_join_kernel(HeadMixParams p) {
+__global__ void __launch_bounds__(256) headmix_join_kernel(HeadMixParams p) {
+  // a thread an output element: its spans' partial results are independent loads, all in flight together
   const int r = blockIdx.x, n = p.Hq * p.D;
-  const float* src = p.partial + (long long)r * p.spans * n;
-  T* out = (T*)p.out + (long long)r * n;
-  const T* gate = p.gate ? (const T*)p.gate + (long long)r * p.ld_gate : nullptr;
-  for (int o = threadIdx.x; o < n; o += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < p.spans; ++s) acc += src[(long long)s * n + o];
-    const float g = gate ? 1.f / (1.f + expf(-to_f32(gate[o / p.D]))) : 1.f;
-    out[o] = from_f32<T>(acc * g);
+  const int o = blockIdx.y * blockDim.x + threadIdx.x;
+  if (o >= n) return;
+  const float* src = p.partial + (long long)r * p.spans * n + o;
+  float acc = 0.f;
+  int s = 0;
+  for (; s + 8 <= p.spans; s += 8) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = src[(long long)(s + i) * n];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc += v[i];
   }
+  for (; s < p.spans; ++s) acc += src[(long long)s * n];
+  const T* gate = p.gate ? (const T*)p.gate + (long long)r * p.ld_gate : nullptr;
+  const float g = gate ? 1.f / (1.f + expf(-to_f32(gate[o / p.D]))) : 1.f;
+  ((T*)p.out)[(long long)r * n + o] = from_f32<T>(acc * g);
 }
 
 template <typename T>
@@ -358,7 +366,7 @@ static int headmix_launch(const HeadMixParams& p, cudaStream_t stream) {
   TL_HM(1);
   TL_HM(2);
 #undef TL_HM
-  headmix_join_kernel<T><<<p.rows, 256, 0, stream>>>(p);
+  headmix_join_kernel<T><<<dim3(p.rows, ceil_div(p.Hq * p.D, 256)), 256, 0, stream>>>(p);
   TL_LAUNCH_CHECK();
   return 0;
 }

@@ -149,7 +149,16 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
   const bool v_lo = r_lo < nq, v_hi = r_hi < nq;
   const int p_lo = pos0 + r_lo, p_hi = pos0 + r_hi;
   const int w_lo = p.window > 0 ? p_lo - p.window + 1 : 0, w_hi = p.window > 0 ? p_hi - p.window + 1 : 0;
+  // (most tiles of a prompt lie before every row of the block and inside every row's window: nothing to mask there)
+  const int open_from = p.window > 0 ? pos0 + nq - p.window : 0;
   auto mask_scale = [&](float (*s)[4], int j0) {
+    if (nq == BM && j0 >= open_from && j0 >= 0 && j0 + TJ - 1 <= pos0) {
+#pragma unroll
+      for (int n = 0; n < 4; ++n) {
+        s[n][0] *= p.scale; s[n][1] *= p.scale; s[n][2] *= p.scale; s[n][3] *= p.scale;
+      }
+      return;
+    }
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
 #pragma unroll

@@ -435,7 +435,7 @@ def attention_join(scratch, positions, window, out, n_spans: int, span_keys: int
           kernels=1 if n_spans > 1 else 0)
 
 
-HEADMIX_SPAN = 64       # the fewest keys a span of `attention_headmix` holds (a step's rows too few to fill the GPU)
+HEADMIX_SPAN = 32       # the fewest keys a span of `attention_headmix` holds: one tile (measured: 40 us a layer at 8 rows and a window of 1024 against 49 with 64 and 82 with 128)
 
 
 _sm_count = None
