@@ -349,6 +349,8 @@ class LaunchTimer:
             if grouped:
                 return "experts gate/up + SwiGLU (tcgen05)" if gated else "experts down (tcgen05)"
             return "dense products (tcgen05, pairs of SMs)"
+        if name == "tl_gemm_tc_pair_act":
+            return "dense products (tcgen05, pairs of SMs, activation in the epilogue)"
         if name == "tl_gemm_skinny_grouped":
             return "experts gate/up + SwiGLU (register-only)" if args[11] else "experts down (register-only)"
         return {"tl_gemm_skinny_mma": "dense products (register-only)", "tl_gemm_skinny_conv": "in-projection + short conv",

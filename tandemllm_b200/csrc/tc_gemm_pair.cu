@@ -48,6 +48,8 @@ struct Params {
   const int* n_tiles;
   int plan_rows;              // the height of the tile map's tiles, at most TOKENS
   int act;                    // the gate's activation (TL_ACT_*), 0 for a plain product
+  int unary;                  // plain product: an activation (TL_ACT_*) applied to every output (after the bias), 0 for none
+  float a0, a1;               // that activation's constants
   int skip_kb;                // -1; a test sets the k-block (counted over a cluster's tiles) whose copies both producers leave out
   int splits;                 // plain, ungrouped: work items a tile, each a run of k-blocks with a 32-bit partial result of its own
   int kb_per_split;           // k-blocks a run (every run holds at least one)
@@ -374,6 +376,19 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j) v[j] += b;
+          if (p.unary == TL_ACT_XIELU) {
+            // written for speed, as the gated epilogue is: both branches from the fast exponential, one select (the
+            // result is rounded to bfloat16, far coarser than exp(z) - 1 - z loses near 0 beside the z / 2 it is added to)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float z = v[j], half = 0.5f * z;
+              const float neg = fmaf(p.a1, __expf(fminf(z, 0.f)) - 1.f - z, half);
+              v[j] = z > 0.f ? fmaf(p.a0 * z, z, half) : neg;
+            }
+          } else if (p.unary) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = activation(v[j], p.unary, p.a0, p.a1);
+          }
         }
         __syncwarp();
 #pragma unroll
@@ -503,12 +518,14 @@ extern "C" int tl_tc_pair_resident(int gated, int per_sm) {
 // 32-bit output): the reduction is cut into `splits` runs of k-blocks, each a work item of its own, and C receives the
 // runs' partial results one behind the other, [splits, M, ldc], for the caller to add in order (a product with fewer
 // tiles than the GPU has pairs of SMs: a pair streams a tile's operands at the rate of its two SMs whatever else is idle).
-extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
-                               long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K,
-                               int gated, int out_dtype, const int* tile_group, const int* tile_row0, const int* tile_rows,
-                               const int* n_tiles, int max_tiles, int plan_rows, int per_sm, int splits, int* status,
-                               cudaStream_t stream) {
+static int pair_product(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
+                        long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K,
+                        int gated, int out_dtype, const int* tile_group, const int* tile_row0, const int* tile_rows,
+                        const int* n_tiles, int max_tiles, int plan_rows, int per_sm, int splits, int unary, float a0, float a1,
+                        int* status, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  TL_REQUIRE(unary >= 0 && unary <= TL_ACT_LAST && (!unary || (!gated && splits == 1)),
+             "pair product: an activation on the outputs (%d) needs the plain product in one run", unary);
   TL_REQUIRE(M > 0 && N > 0 && K > 0, "pair product: M %d N %d K %d", M, N, K);
   TL_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0,
              "pair product: K %d and the row strides %lld, %lld must be multiples of 8 elements (16 bytes) for TMA", K, ldx, ldw);
@@ -538,6 +555,7 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles;
   p.plan_rows = plan_rows;
   p.act = gated; p.status = status;
+  p.unary = unary; p.a0 = a0; p.a1 = a1;
   p.skip_kb = pair::skip_kb_for_test();
   p.splits = splits; p.kb_per_split = kb_per_split; p.part_stride = splits > 1 ? (long long)M * ldc : 0;
   const long long work = (long long)ceil_div(N, 2 * pair::ROWS) * (tile_group ? max_tiles : ceil_div(M, tokens)) * splits;
@@ -546,6 +564,24 @@ extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, c
   if (per_sm == 2) return gated ? TL_PAIR(true, 2) : TL_PAIR(false, 2);
   return gated ? TL_PAIR(true, 1) : TL_PAIR(false, 1);
 #undef TL_PAIR
+}
+
+extern "C" int tl_gemm_tc_pair(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
+                               long long rows_per_group, const float* bias, void* C, long long ldc, int M, int N, int K,
+                               int gated, int out_dtype, const int* tile_group, const int* tile_row0, const int* tile_rows,
+                               const int* n_tiles, int max_tiles, int plan_rows, int per_sm, int splits, int* status,
+                               cudaStream_t stream) {
+  return pair_product(X, ldx, x_rows, W, ldw, w_rows, rows_per_group, bias, C, ldc, M, N, K, gated, out_dtype, tile_group,
+                      tile_row0, tile_rows, n_tiles, max_tiles, plan_rows, per_sm, splits, 0, 0.f, 0.f, status, stream);
+}
+
+// C = act(X W^T + bias): the plain, ungrouped product with an activation (TL_ACT_*, constants a0 and a1) in its epilogue.
+extern "C" int tl_gemm_tc_pair_act(const void* X, long long ldx, long long x_rows, const void* W, long long ldw, long long w_rows,
+                                   const float* bias, void* C, long long ldc, int M, int N, int K, int out_dtype, int act,
+                                   float a0, float a1, int* status, cudaStream_t stream) {
+  TL_REQUIRE(act >= 1 && act <= TL_ACT_LAST, "pair product: activation %d is not one of 1..%d", act, TL_ACT_LAST);
+  return pair_product(X, ldx, x_rows, W, ldw, w_rows, 0, bias, C, ldc, M, N, K, 0, out_dtype, nullptr, nullptr, nullptr, nullptr,
+                      0, 0, 1, 1, act, a0, a1, status, stream);
 }
 
 // For tests of the bounded waits, as in tc_gemm.cu: the polls after which an mbarrier wait of this file's kernel gives up

@@ -67,6 +67,10 @@ def lib():
                                       c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
         l.tl_gemm_tc_pair.restype = c_int
+        l.tl_gemm_tc_pair_act.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p,
+                                          c_longlong, c_int, c_int, c_int, c_int, c_int, ctypes.c_float, ctypes.c_float, c_void_p,
+                                          c_void_p]
+        l.tl_gemm_tc_pair_act.restype = c_int
         l.tl_tc_pair_token_tile.argtypes = [c_int]
         l.tl_tc_pair_token_tile.restype = c_int
         l.tl_gather_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]
@@ -267,9 +271,17 @@ class TensorCore:
         return self.gemm(x, w, bias, out, defer=defer) or True
 
     def linear_act(self, x, w, act: int, a0: float = 0.0, a1: float = 0.0):
-        """act(x @ w^T) in bfloat16 with the activation in the product's epilogue, or None when no kernel here does it
-        for these operands (the caller then runs the product and the activation one after the other)."""
-        return None
+        """act(x @ w^T) in bfloat16 with the activation in the epilogue of the prompt-sized product (pairs of SMs), or None
+        when that kernel does not take these operands: a decode step's few rows, strides TMA cannot box (the caller then
+        runs the product and the activation one after the other, as a gated feed-forward does for a decode step)."""
+        M, N = x.shape[0], w.shape[0]
+        if M <= 128 or PROMPT_PRODUCT != "pair" or not usable(x, w) or N % 8:
+            return None
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        _check(lib().tl_gemm_tc_pair_act(x.data_ptr(), x.stride(0), x.shape[0], w.data_ptr(), w.stride(0), w.shape[0], None,
+                                         out.data_ptr(), out.stride(0), M, N, x.shape[1], ops.dtype_code(out.dtype), int(act),
+                                         float(a0), float(a1), self.status.data_ptr(), ops.stream()), "gemm_tc_pair_act")
+        return out
 
     def attention_headmix(self, q, cache, table, step, scale, window, mix, gate, ld_gate, out, runtime) -> bool:
         """Attention with the heads' weights mixed after the softmax on the tensor cores (csrc/attention_headmix_mma.cu), for

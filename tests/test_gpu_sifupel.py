@@ -425,3 +425,23 @@ def test_head_mixed_attention_on_the_tensor_cores(H, G, D, window, T_):
     torch.cuda.synchronize()
     assert int(rt.status.item()) == 0
     assert rel(out.float().view(rows, -1), want[first:].reshape(rows, -1)) < 2e-2
+
+
+def test_the_activation_in_the_prompt_products_epilogue():
+    """The ungated feed-forward's up product with xIELU applied to the 32-bit accumulator before it is rounded, against
+    the plain activation of the plain product; a decode step's few rows are told to take the unfused way."""
+    from tandemllm_b200.kernels import ops, tensorcore
+    from tandemllm_b200.parts.base import Runtime
+    dev = torch.device("cuda")
+    rt = Runtime(dev, torch.bfloat16)
+    tc = tensorcore.enable(rt)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(300, 136, generator=g).to(torch.bfloat16)
+    w = (torch.randn(200, 136, generator=g) * 0.2).to(torch.bfloat16)
+    pq = torch.tensor([0.3, -0.4])
+    sp = torch.nn.functional.softplus(pq)
+    got = tc.linear_act(x.to(dev), w.to(dev), ops.ACTIVATIONS["xielu"], float(sp[0]), float(0.5 + sp[1]))
+    assert got is not None and int(rt.status.item()) == 0
+    want = P.xielu(x.double() @ w.double().T, pq.double())
+    assert rel(got.float(), want) < 1e-2
+    assert tc.linear_act(x[:8].to(dev), w.to(dev), ops.ACTIVATIONS["xielu"], 1.0, 1.0) is None
