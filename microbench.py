@@ -6,6 +6,8 @@
     python microbench.py attention --batch 8 --context 8192
     python microbench.py attention --batch 1 --rows 2048 --context 2048
     python microbench.py norm --rows 8
+    python microbench.py headmix --batch 8 --window 1024
+    python microbench.py headmix --batch 1 --rows 2048 --window 1024
 
 Sizes default to the LFM2-8B-A1B layer (hidden 2048, 32 experts of width 1792 top-4, 32/8 heads of 64). Inputs are
 larger than the 126 MB L2 or a 256 MB buffer is written between timed launches, so DRAM figures mean something; a
@@ -147,6 +149,47 @@ def norm(a) -> dict:
     return {"kernel": "residual add + RMS norm", "rows": R, "hidden": H, "ms": ms, "bytes": nbytes, "GBps": nbytes / ms / 1e6}
 
 
+def headmix(a) -> dict:
+    """Attention with the heads' weights mixed after the softmax: `--rows` 1 is a decode step of `--batch` requests whose
+    windows are full (the CUDA-core kernels, keys cut into spans), more rows a prompt portion (the tensor-core kernel)."""
+    from tandemllm_b200.kernels import ops, tensorcore
+    rt = runtime()
+    H, G, D, win, B, R = a.heads, a.kv_heads, a.head_dim, a.window, a.batch, a.rows
+    ctx = win + R
+    pages_per = -(-ctx // 16) + 1
+    pool = B * pages_per
+    kc = torch.randn(pool, G, 16, D, device=DEV).to(torch.bfloat16)
+    vc = torch.randn(pool, G, 16, D, device=DEV).to(torch.bfloat16)
+    table = torch.arange(pool, dtype=torch.int32, device=DEV).view(B, pages_per).contiguous()
+    mix = (torch.eye(H) + 0.1 * torch.randn(H, H)).to(DEV)
+    q = torch.randn(B * R, H, D, device=DEV).to(torch.bfloat16)
+    gate = torch.randn(B * R, H, device=DEV).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    pos = (torch.arange(R, dtype=torch.int32) + win).repeat(B).to(DEV)
+    req = torch.arange(B, dtype=torch.int32).repeat_interleave(R).to(DEV)
+    pairs = B * sum(min(win + i + 1, win) for i in range(R))
+    if R == 1:
+        fn = lambda: ops.attention_headmix(q, kc, vc, table, 16, req, pos, D ** -0.5, win, mix, gate, H, out, ctx, rt, rt.status)
+        kernel = "head-mixed attention, CUDA cores (statistics, apply, join)"
+    else:
+        lib = tensorcore.lib()
+        if not lib.tl_attention_headmix_mma_supported(H, G, D):
+            raise SystemExit(f"the tensor-core kernel does not take {H} heads over {G} of size {D}")
+        tiles = torch.tensor([(b, b * R + r0, min(16, R - r0)) for b in range(B) for r0 in range(0, R, 16)],
+                             dtype=torch.int32, device=DEV)
+        fn = lambda: lib.tl_attention_headmix_mma(
+            q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), table.shape[1], 16, pool, tiles.data_ptr(),
+            tiles.shape[0], pos.data_ptr(), D ** -0.5, win, mix.data_ptr(), gate.data_ptr(), H, out.data_ptr(), H, G, D,
+            rt.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        kernel = "head-mixed attention, mma.sync (prompt portions)"
+    ms = timed(fn, a.iters)
+    assert int(rt.status.item()) == 0
+    flops = 4.0 * pairs * H * D + 2.0 * pairs * H * H
+    nbytes = 2.0 * 2 * B * min(ctx, win + R - 1) * G * D
+    return {"kernel": kernel, "batch": B, "rows": R, "window": win, "heads": H, "kv_heads": G, "head_dim": D, "ms": ms,
+            "flops": flops, "TFLOPs": flops / ms / 1e9, "kv_bytes": nbytes, "GBps": nbytes / ms / 1e6}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -175,16 +218,23 @@ def main(argv=None) -> int:
                    help="the tcgen05 kernel: P as the MMA's operand from tensor memory, or through shared memory")
     t.add_argument("--copies", default="tma", choices=("tma", "cp.async"),
                    help="decoding with the mma kernel: a producer warp's TMA copies, or cp.async from every thread")
+    hm = sub.add_parser("headmix")
+    hm.add_argument("--batch", type=int, default=8)
+    hm.add_argument("--rows", type=int, default=1)
+    hm.add_argument("--window", type=int, default=1024)
+    hm.add_argument("--heads", type=int, default=32)
+    hm.add_argument("--kv-heads", type=int, default=8)
+    hm.add_argument("--head-dim", type=int, default=64)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=2048)
     for p in (e, d):
         p.add_argument("--product", default="pair", choices=("pair", "single"),
                        help="prompt-sized products: the kernel on pairs of SMs (cta_group::2), or the one-CTA persistent kernel")
-    for p in (e, d, t, n):
+    for p in (e, d, t, n, hm):
         p.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)
-    result = {"expert_gemm": expert_gemm, "dense_gemm": dense_gemm, "attention": attention, "norm": norm}[a.what](a)
+    result = {"expert_gemm": expert_gemm, "dense_gemm": dense_gemm, "attention": attention, "norm": norm, "headmix": headmix}[a.what](a)
     print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in result.items()}))
     return 0
 
