@@ -56,7 +56,7 @@ def random_weights(specs: Iterable[TensorSpec], seed: int, std: float = 0.02, bi
 
 
 def write_model_folder(config, folder: str, seed: int, std: float = 0.02, bias_std: float = 0.1, norm_std: float = 0.0,
-                       dtype: torch.dtype = torch.bfloat16, name_prefix: str = "model.") -> str:
+                       dtype: torch.dtype = torch.bfloat16, name_prefix: str | None = None) -> str:
     """Write `folder/config.json` and `folder/model.safetensors` for the typed `config` (anything with
     `to_dict()` and `to_spec()`), random weights from `seed`. Matrices are stored in `dtype`; vectors that the
     engine keeps in 32-bit (the expert bias) are stored in 32-bit when `dtype` is float32, else in `dtype`,
@@ -64,6 +64,8 @@ def write_model_folder(config, folder: str, seed: int, std: float = 0.02, bias_s
     from ..parts.model import DecoderModel      # the parts say which tensors a model reads
     os.makedirs(folder, exist_ok=True)
     spec = config.to_spec()
+    if name_prefix is None:         # what the architecture's stored names carry in front (none for some)
+        name_prefix = spec.name_prefixes[0] if spec.name_prefixes else ""
     model = DecoderModel(spec)
     tensors = {}
     for s in model.weight_specs(None):

@@ -84,3 +84,22 @@ def test_the_head_mix_with_the_identity_is_ordinary_attention():
         outs.append(torch.softmax(s, -1) @ kr[:, c] * torch.sigmoid(n @ W["l0.mix.g"].double().T)[:, h:h + 1])
     want = torch.cat(outs, -1) @ W["l0.mix.o"].double().T
     assert torch.allclose(got, want, atol=1e-10)
+
+
+def test_the_command_line_writes_and_audits_a_folder_of_this_design(tmp_path):
+    import json
+
+    from tandemllm_b200.__main__ import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(S.S1))
+    out = tmp_path / "model"
+    assert main(["random-weights", "--config", str(cfg), "--seed", "3", "--out", str(out)]) == 0
+    from tandemllm_b200.config import read_model_config, spec_of
+    from tandemllm_b200.parts.model import DecoderModel
+    from tandemllm_b200.weights.loader import FolderWeights
+    arch, config = read_model_config(str(out))
+    spec = spec_of(config)
+    weights = FolderWeights(str(out), spec.name_prefixes)
+    weights.check(DecoderModel(spec).weight_specs(weights.present()))
+    assert arch.name == "sifupel" and set(weights.present()) == set(S.tensor_shapes(S.S1))
+    assert main(["audit", "--model", str(out)]) == 0
