@@ -7,6 +7,9 @@ s2: widths and head sizes that the tensor-core kernels of the bfloat16 path take
     windows of 70 and 48 (a page's multiple).
 s3: a head size of 128, a window longer than any test's sequence (nothing is ever masked but the future), and a layer
     whose window is exactly four pages.
+s4: sizes no kernel is tuned for: an odd vocabulary and a width that is no multiple of 8, head sizes of 20, 72, 40 and 256,
+    one head, five heads that are their own KV heads, forty heads over eight KV heads (more than the tensor-core kernel
+    takes), feed-forward widths that are no multiples of 8, windows of 100, 7, 64 and 3, six layers, two without a feed-forward.
 No scale equals dim^-1/2, eps differs, and the norms' alpha, weight and bias are random.
 """
 
@@ -30,8 +33,11 @@ S2 = {"architecture": "Sifupel", "vocab": 320, "width": 128, "norm": {"eps": 1e-
       "layers": [_attn(4, 2, 64, 70, 0.2, 192), _attn(8, 4, 32, 48, 0.11, 256)]}
 S3 = {"architecture": "Sifupel", "vocab": 130, "width": 64, "norm": {"eps": 1e-5},
       "layers": [_attn(2, 1, 128, 300, 0.05, 96), _attn(2, 2, 32, 64, 0.4, 72)]}
-CONFIGS = {"s1": S1, "s2": S2, "s3": S3}
-SEEDS = {"s1": 11, "s2": 12, "s3": 13}
+S4 = {"architecture": "Sifupel", "vocab": 1001, "width": 100, "norm": {"eps": 3e-6},
+      "layers": [_attn(5, 5, 20, 100, 0.21, 136), _attn(1, 1, 72, 7, 0.09, None), _attn(12, 3, 40, 64, 0.13, 28),
+                 _attn(40, 8, 64, 50, 0.12, 44), _attn(2, 2, 256, 3, 0.06, None), _attn(9, 3, 48, 31, 0.19, 60)]}
+CONFIGS = {"s1": S1, "s2": S2, "s3": S3, "s4": S4}
+SEEDS = {"s1": 11, "s2": 12, "s3": 13, "s4": 14}
 
 
 def tensor_shapes(cfg: dict) -> dict[str, tuple]:

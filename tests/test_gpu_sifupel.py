@@ -271,7 +271,7 @@ def cuts(n, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["s1", "s2", "s3"])
+@pytest.mark.parametrize("name", ["s1", "s2", "s3", "s4"])
 def test_whole_prompts_decoding_and_portions_agree_with_the_plain_model(name, dtype, plain_logits):
     engine, cfg, W = engine_of(name, dtype)
     toks = S.tokens(name, 150, seed=3)
@@ -297,7 +297,7 @@ def test_whole_prompts_decoding_and_portions_agree_with_the_plain_model(name, dt
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["s1", "s2"])
+@pytest.mark.parametrize("name", ["s1", "s2", "s4"])
 def test_unequal_requests_in_one_batch_on_pages_and_slots_that_are_used_again(name, dtype, plain_logits):
     """Seven requests of unequal length through four slots and a pool too small for all of them: portions beside
     single tokens, requests that pause, pages and slots that come back and are taken again."""

@@ -40,7 +40,7 @@ def test_values_that_do_not_fit_are_refused():
             SifupelConfig.from_dict(raw)
 
 
-@pytest.mark.parametrize("name", ["s1", "s2", "s3"])
+@pytest.mark.parametrize("name", ["s1", "s2", "s3", "s4"])
 def test_the_parts_read_the_designs_tensors_and_no_others(name):
     from tandemllm_b200.config import SifupelConfig
     from tandemllm_b200.parts.model import DecoderModel
