@@ -3,8 +3,9 @@
 //   s_g(i, j) = scale * <q_g(i), k_c(g)(j)>,  p_g = softmax_j s_g over the keys row i sees (its window),
 //   p'_h = sum_g M[h, g] p_g,   o_h(i) = sigmoid(gate_h(i)) * sum_j p'_h(i, j) v_c(h)(j)
 //
-// One block of eight warps takes 16 consecutive query rows of one request and ALL heads, because the mix needs every
-// head's finished softmax at a (row, key). A warp owns up to HPW heads (head = warp + 8 i). Keys are visited in tiles of
+// One block of NW (eight or sixteen) warps takes 16 consecutive query rows of one request and ALL heads, because the mix
+// needs every head's finished softmax at a (row, key). A warp owns up to HPW heads (head = warp + NW i); sixteen warps
+// where eight would hold four heads' outputs each (one block an SM either way: twice the warps to cover latencies). Keys are visited in tiles of
 // 32 aligned to absolute positions, twice:
 //   pass 1   S = Q K^T on the tensor cores, each head's running maximum and sum a row in registers (32-bit)
 //   pass 2   S again; p = exp(s - max) / sum in 32-bit into shared memory; every thread mixes the heads of its (row, key)
@@ -21,7 +22,6 @@ constexpr int BM = 16;          // query rows a block
 constexpr int TJ = 32;          // keys a tile
 constexpr int PS = 40;          // floats a row of a head's weight tile (16 x 32 used): 64-bit accesses of a half warp
                                 // (rows r .. r + 3, four column pairs each) then fall into 32 different banks
-constexpr int THREADS = 256;
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp16(void* dst, const void* src, bool valid) {
@@ -68,10 +68,11 @@ template <int D> __host__ __device__ inline size_t smem_bytes(int Hq, int Hk) {
   return (size_t)Hq * BM * D * 2 + (size_t)2 * Hk * TJ * D * 2 + (size_t)Hq * BM * PS * 4 + hq_max * hq_max * 4;
 }
 
-template <int D, int HPW>
-__global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_kernel(Params p) {
+template <int D, int HPW, int NW>
+__global__ void __launch_bounds__(NW * 32, (NW == 16 || HPW * D >= 256) ? 1 : 2) headmix_mma_kernel(Params p) {
+  constexpr int THREADS = NW * 32;
   constexpr int CH = D / 8;                    // 16-byte chunks a row
-  constexpr int HQMAX = 8 * HPW;
+  constexpr int HQMAX = NW * HPW;
   extern __shared__ __align__(128) uint8_t hmm_smem[];
   const int Hq = p.Hq, Hk = p.Hk, group = Hq / Hk;
   uint8_t* sQ = hmm_smem;                                       // [Hq][16][D] bf16
@@ -99,13 +100,15 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
   }
 
   // A thread copies the same 16-byte chunk of the same key for every KV head: the key's page is looked up once a tile.
-  static_assert(THREADS % CH == 0 && (TJ * CH) % THREADS == 0, "whole keys a round of the block's threads");
+  constexpr int STAGERS = THREADS < TJ * CH ? THREADS : TJ * CH;        // threads that copy (a block may have more than chunks)
+  static_assert(STAGERS % CH == 0 && (TJ * CH) % STAGERS == 0, "whole keys a round of the copying threads");
   const long long kv_head_stride = (long long)p.page_size * D;
   auto stage = [&](const bf16* cache, uint8_t* dst, int j0) {
+    if (tid >= STAGERS) return;
     const int c = tid % CH;
 #pragma unroll
-    for (int rnd = 0; rnd < TJ * CH / THREADS; ++rnd) {
-      const int jj = tid / CH + rnd * (THREADS / CH);
+    for (int rnd = 0; rnd < TJ * CH / STAGERS; ++rnd) {
+      const int jj = tid / CH + rnd * (STAGERS / CH);
       const int kp = j0 + jj;
       bool valid = kp >= k_lo && kp <= k_hi;
       long long off = 0;
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
     const uint8_t* keys = cur ? sV : sK;
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
-      const int g = warp + 8 * i;
+      const int g = warp + NW * i;
       if (g < Hq) {
         float s[4][4];
         qk(g, keys, s);
@@ -259,7 +262,7 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
-      const int g = warp + 8 * i;
+      const int g = warp + NW * i;
       if (g < Hq) {
         float s[4][4];
         qk(g, sK, s);
@@ -281,16 +284,17 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
       cp_commit();
     }
     if (p.mix) {
-      // a thread owns two (row, key) places and mixes all heads there: p'_h = sum_g M[h, g] p_g, in place. The mix's
-      // rows are read 16 bytes at a time (the same address for every thread), each value used for both places.
-      static_assert(BM * TJ == 2 * THREADS, "two places a thread");
+      // a thread owns one or two (row, key) places and mixes all heads there: p'_h = sum_g M[h, g] p_g, in place. The
+      // mix's rows are read 16 bytes at a time (the same address for every thread), each value used for every place.
+      constexpr int PLACES = BM * TJ / THREADS;
+      static_assert(PLACES == 1 || PLACES == 2, "one or two places a thread");
       float* at0 = sP + (tid / TJ) * PS + tid % TJ;
       float* at1 = at0 + (THREADS / TJ) * PS;
-      float pa[HQMAX], pb[HQMAX];
+      float pa[HQMAX], pb[PLACES == 2 ? HQMAX : 1];
 #pragma unroll
       for (int g = 0; g < HQMAX; ++g) {
         pa[g] = g < Hq ? at0[(size_t)g * BM * PS] : 0.f;
-        pb[g] = g < Hq ? at1[(size_t)g * BM * PS] : 0.f;
+        if constexpr (PLACES == 2) pb[g] = g < Hq ? at1[(size_t)g * BM * PS] : 0.f;
       }
       for (int h = 0; h < Hq; ++h) {
         const float4* mh = reinterpret_cast<const float4*>(sM + h * HQMAX);
@@ -298,13 +302,15 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
 #pragma unroll
         for (int g4 = 0; g4 < HQMAX / 4; ++g4) {
           const float4 m4 = mh[g4];
-          acc_a = fmaf(m4.x, pa[4 * g4], acc_a); acc_b = fmaf(m4.x, pb[4 * g4], acc_b);
-          acc_a = fmaf(m4.y, pa[4 * g4 + 1], acc_a); acc_b = fmaf(m4.y, pb[4 * g4 + 1], acc_b);
-          acc_a = fmaf(m4.z, pa[4 * g4 + 2], acc_a); acc_b = fmaf(m4.z, pb[4 * g4 + 2], acc_b);
-          acc_a = fmaf(m4.w, pa[4 * g4 + 3], acc_a); acc_b = fmaf(m4.w, pb[4 * g4 + 3], acc_b);
+          acc_a = fmaf(m4.x, pa[4 * g4], acc_a); acc_a = fmaf(m4.y, pa[4 * g4 + 1], acc_a);
+          acc_a = fmaf(m4.z, pa[4 * g4 + 2], acc_a); acc_a = fmaf(m4.w, pa[4 * g4 + 3], acc_a);
+          if constexpr (PLACES == 2) {
+            acc_b = fmaf(m4.x, pb[4 * g4], acc_b); acc_b = fmaf(m4.y, pb[4 * g4 + 1], acc_b);
+            acc_b = fmaf(m4.z, pb[4 * g4 + 2], acc_b); acc_b = fmaf(m4.w, pb[4 * g4 + 3], acc_b);
+          }
         }
         at0[(size_t)h * BM * PS] = acc_a;
-        at1[(size_t)h * BM * PS] = acc_b;
+        if constexpr (PLACES == 2) at1[(size_t)h * BM * PS] = acc_b;
       }
     }
     if (more) cp_wait<1>();             // this tile's values (the next tile's keys may still be on their way)
@@ -312,7 +318,7 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < HPW; ++i) {
-      const int h = warp + 8 * i;
+      const int h = warp + NW * i;
       if (h < Hq) {
         const float* ph = sP + (size_t)h * BM * PS;
         const uint8_t* v_tile = sV + (size_t)(h / group) * TJ * D * 2;
@@ -345,7 +351,7 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
   // ---- gate and store ----
 #pragma unroll
   for (int i = 0; i < HPW; ++i) {
-    const int h = warp + 8 * i;
+    const int h = warp + NW * i;
     if (h < Hq) {
       float g_lo = 1.f, g_hi = 1.f;
       if (p.gate) {
@@ -364,16 +370,16 @@ __global__ void __launch_bounds__(THREADS, HPW * D >= 256 ? 1 : 2) headmix_mma_k
   }
 }
 
-template <int D, int HPW>
+template <int D, int HPW, int NW>
 static int launch(const Params& p, int n_tiles, cudaStream_t stream) {
   const size_t smem = smem_bytes<D>(p.Hq, p.Hk);
   static bool set = false;
   if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<D, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<D, HPW, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return (int)e;
     set = true;
   }
-  headmix_mma_kernel<D, HPW><<<n_tiles, THREADS, smem, stream>>>(p);
+  headmix_mma_kernel<D, HPW, NW><<<n_tiles, NW * 32, smem, stream>>>(p);
   TL_LAUNCH_CHECK();
   return 0;
 }
@@ -409,12 +415,14 @@ extern "C" int tl_attention_headmix_mma(const void* q, const void* k_cache, cons
   p.max_pages = max_pages; p.page_size = page_size; p.num_pages = num_pages; p.tiles = tiles; p.positions = positions;
   p.scale = scale; p.window = window; p.mix = mix; p.gate = (const bf16*)gate; p.ld_gate = ld_gate; p.out = (bf16*)out;
   p.Hq = Hq; p.Hk = Hk; p.status = status;
-  const int hpw = (Hq + 7) / 8;
   if (D == 64) {
-    if (hpw <= 1) return hmm::launch<64, 1>(p, n_tiles, stream);
-    if (hpw <= 2) return hmm::launch<64, 2>(p, n_tiles, stream);
-    return hmm::launch<64, 4>(p, n_tiles, stream);
+    if (Hq <= 8) return hmm::launch<64, 1, 8>(p, n_tiles, stream);
+    if (Hq <= 16) return hmm::launch<64, 2, 8>(p, n_tiles, stream);
+    // up to 32 heads: eight warps of four heads each (sixteen warps of two heads measured the same, 5.03 against 4.97 ms
+    // for twelve layers of a 2048-token prompt: this case is not short of warps)
+    return hmm::launch<64, 4, 8>(p, n_tiles, stream);
   }
-  if (hpw <= 1) return hmm::launch<128, 1>(p, n_tiles, stream);
-  return hmm::launch<128, 2>(p, n_tiles, stream);
+  if (Hq <= 8) return hmm::launch<128, 1, 8>(p, n_tiles, stream);
+  // up to 16 heads of 128: sixteen warps, one head each (5.61 against 6.21 ms with eight warps of two heads)
+  return hmm::launch<128, 1, 16>(p, n_tiles, stream);
 }
