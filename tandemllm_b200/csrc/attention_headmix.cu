@@ -13,6 +13,8 @@
 // row's position alone: not on how a prompt was cut, on the batch, or on the pages. With one span a single kernel does
 // both passes; with several (long contexts, few rows) a first kernel leaves every span's maximum and sum, a second joins
 // them, applies its span and leaves partial outputs, and a third adds those in span order.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace tl {
@@ -103,9 +105,6 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
   constexpr int VEC = 16 / (int)sizeof(T);
   const bool vec_ok = D % VEC == 0;
   const long long head_stride = (long long)p.page_size * D;
-  // heads a unit of work takes together against one key (they share the key's row): as many as keep every warp busy
-  const int hb = max(1, min(min(8, group), (Hq + nwarps - 1) / nwarps));
-  const int blocks_per_group = (group + hb - 1) / hb;
 
   // where the tile's keys lie (KV head 0; -1: not visible from this block, or no page)
   auto locate = [&](int j0) {
@@ -120,15 +119,21 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
       rowoff[tid] = off;
     }
   };
-  // the tile's rows of KV heads c0 .. c0 + nc - 1 from `cache` into `dst` (rows that are not seen become zeros)
+  // the tile's rows of KV heads c0 .. c0 + nc - 1 from `cache` into `dst` (rows that are not seen become zeros); a thread
+  // takes the same 16-byte piece of the same key for every KV head, so a piece's place is worked out once
   auto stage = [&](const T* cache, T* dst, int c0, int nc) {
     if (vec_ok) {
-      const int per_row = D / VEC, n = nc * HM_TILE * per_row;
-      for (int i = tid; i < n; i += HM_THREADS) {
-        const int ch = i % per_row, jj = (i / per_row) % HM_TILE, cc = i / (per_row * HM_TILE);
+      const int per_row = D / VEC;
+      for (int i = tid; i < HM_TILE * per_row; i += HM_THREADS) {
+        const int jj = i / per_row, ch = i - jj * per_row;
         const long long off = rowoff[jj];
-        const T* src = cache + (off < 0 ? 0 : off + (long long)(c0 + cc) * head_stride + ch * VEC);
-        hm_cp_async16(dst + ((size_t)cc * HM_TILE + jj) * DP + ch * VEC, src, off >= 0);
+        const T* src = cache + (off < 0 ? 0 : off + (long long)c0 * head_stride + ch * VEC);
+        T* to = dst + (size_t)jj * DP + ch * VEC;
+        for (int cc = 0; cc < nc; ++cc) {
+          hm_cp_async16(to, src, off >= 0);
+          to += (size_t)HM_TILE * DP;
+          if (off >= 0) src += head_stride;
+        }
       }
     } else {
       const int n = nc * HM_TILE * D;
@@ -140,16 +145,19 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
     }
   };
   // Scores of the heads of KV heads c0 .. c0 + nc - 1 against the staged keys, a key a lane; `use(g, s)` is called by the
-  // whole warp with head g's score of the lane's key (-inf where the key is not seen).
-  auto scores = [&](int c0, int nc, auto&& use) {
+  // whole warp with head g's score of the lane's key (-inf where the key is not seen). HB heads of a group share each
+  // piece of the key's row (HB divides the group, so the loops over them unroll without guards).
+  auto scores_of = [&](auto hb_tag, int c0, int nc, auto&& use) {
+    constexpr int HB = decltype(hb_tag)::value;
+    const int blocks = group / HB;
     const bool seen = rowoff[lane] >= 0;
-    for (int u = warp; u < nc * blocks_per_group; u += nwarps) {
-      const int cc = u / blocks_per_group, g0 = (c0 + cc) * group + (u % blocks_per_group) * hb;
-      const int nh = min(hb, (c0 + cc + 1) * group - g0);
+    for (int u = warp; u < nc * blocks; u += nwarps) {
+      const int cc = u / blocks, g0 = (c0 + cc) * group + (u - cc * blocks) * HB;
       const T* krow = sK + ((size_t)cc * HM_TILE + lane) * DP;
-      float acc[8];
+      const float* q0 = qs + (size_t)g0 * D;
+      float acc[HB];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int i = 0; i < HB; ++i) acc[i] = 0.f;
       if (vec_ok) {
         for (int d = 0; d < D; d += VEC) {
           const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
@@ -158,15 +166,13 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
 #pragma unroll
           for (int x = 0; x < VEC; ++x) f[x] = to_f32(e[x]);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (i < nh) {
-              const float* qg = qs + (size_t)(g0 + i) * D + d;
+          for (int i = 0; i < HB; ++i) {
+            const float* qg = q0 + (size_t)i * D + d;
 #pragma unroll
-              for (int x = 0; x < VEC; x += 4) {
-                const float4 q4 = *reinterpret_cast<const float4*>(qg + x);
-                acc[i] = fmaf(q4.x, f[x], acc[i]); acc[i] = fmaf(q4.y, f[x + 1], acc[i]);
-                acc[i] = fmaf(q4.z, f[x + 2], acc[i]); acc[i] = fmaf(q4.w, f[x + 3], acc[i]);
-              }
+            for (int x = 0; x < VEC; x += 4) {
+              const float4 q4 = *reinterpret_cast<const float4*>(qg + x);
+              acc[i] = fmaf(q4.x, f[x], acc[i]); acc[i] = fmaf(q4.y, f[x + 1], acc[i]);
+              acc[i] = fmaf(q4.z, f[x + 2], acc[i]); acc[i] = fmaf(q4.w, f[x + 3], acc[i]);
             }
           }
         }
@@ -174,14 +180,21 @@ __global__ void __launch_bounds__(HM_THREADS) headmix_attention_kernel(HeadMixPa
         for (int d = 0; d < D; ++d) {
           const float f = to_f32(krow[d]);
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (i < nh) acc[i] = fmaf(qs[(size_t)(g0 + i) * D + d], f, acc[i]);
+          for (int i = 0; i < HB; ++i) acc[i] = fmaf(q0[(size_t)i * D + d], f, acc[i]);
         }
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (i < nh) use(g0 + i, seen ? acc[i] * p.scale : -INFINITY);
+      for (int i = 0; i < HB; ++i) use(g0 + i, seen ? acc[i] * p.scale : -INFINITY);
     }
+  };
+  // as many heads together as keep every warp busy, a power of two that divides the group
+  int hb = 1;
+  while (hb < 8 && group % (2 * hb) == 0 && 2 * hb <= (Hq + nwarps - 1) / nwarps) hb *= 2;
+  auto scores = [&](int c0, int nc, auto&& use) {
+    if (hb == 8) scores_of(std::integral_constant<int, 8>{}, c0, nc, use);
+    else if (hb == 4) scores_of(std::integral_constant<int, 4>{}, c0, nc, use);
+    else if (hb == 2) scores_of(std::integral_constant<int, 2>{}, c0, nc, use);
+    else scores_of(std::integral_constant<int, 1>{}, c0, nc, use);
   };
   const bool whole = kc >= Hk;        // every KV head's tile fits at once: keys and values are staged together
 
