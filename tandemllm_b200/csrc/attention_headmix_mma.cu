@@ -373,11 +373,9 @@ __global__ void __launch_bounds__(NW * 32, (NW == 16 || HPW * D >= 256) ? 1 : 2)
 template <int D, int HPW, int NW>
 static int launch(const Params& p, int n_tiles, cudaStream_t stream) {
   const size_t smem = smem_bytes<D>(p.Hq, p.Hk);
-  static bool set = false;
-  if (!set) {
-    cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<D, HPW, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (smem > 48 * 1024) {          // (asked for at every launch: the attribute belongs to the current device)
+    cudaError_t e = cudaFuncSetAttribute(headmix_mma_kernel<D, HPW, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    set = true;
   }
   headmix_mma_kernel<D, HPW, NW><<<n_tiles, NW * 32, smem, stream>>>(p);
   TL_LAUNCH_CHECK();

@@ -129,7 +129,7 @@ def _plain_headmix(q, k, v, scale, window, mix, gate):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,G,D,window,T_", [(4, 2, 16, 5, 70), (3, 3, 24, 33, 100), (6, 1, 8, 1, 40), (8, 2, 64, 40, 130),
+@pytest.mark.parametrize("H,G,D,window,T_", [(4, 2, 16, 5, 70), (3, 3, 24, 33, 100), (6, 1, 8, 1, 40), (8, 4, 64, 45, 130),
                                                (4, 4, 20, 0, 90), (2, 1, 64, 0, 1500)])
 def test_head_mixed_attention_kernel(dtype, H, G, D, window, T_):
     """All rows of a sequence at once (a prompt), then the last rows one at a time against many keys (decoding: few
@@ -389,8 +389,8 @@ def test_the_replay_program_on_a_folder(dtype, tmp_path, plain_logits):
     assert not (out / "2.f32").exists()
 
 
-@pytest.mark.parametrize("H,G,D,window,T_", [(8, 2, 64, 40, 150), (4, 1, 64, 0, 100), (16, 4, 64, 70, 120), (32, 8, 64, 33, 90),
-                                               (12, 4, 128, 50, 130), (3, 3, 128, 1, 40)])
+@pytest.mark.parametrize("H,G,D,window,T_", [(8, 4, 64, 45, 150), (4, 1, 64, 0, 100), (16, 4, 64, 70, 120), (32, 8, 64, 33, 90),
+                                               (24, 6, 64, 64, 110), (12, 4, 128, 50, 130), (10, 5, 128, 97, 140), (3, 3, 128, 1, 40)])
 def test_head_mixed_attention_on_the_tensor_cores(H, G, D, window, T_):
     """The prompt kernel of the bfloat16 path at its own entry point: tiles of 16 rows and a last, shorter one, a second
     request that begins in the middle of a page's worth of rows, every number of heads a warp (1, 2, 4), windows' edges
