@@ -135,8 +135,9 @@ class CacheManager:
             for gi, g in enumerate(self.groups):
                 shape = (num_pages, g.need.kv_heads, page_size, g.need.head_dim)
                 for i in g.sites:
-                    self.site_cache[i] = PagedSiteCache(gi, page_size, torch.zeros(shape, dtype=dtype, device=device),
-                                                        torch.zeros(shape, dtype=dtype, device=device))
+                    k = torch.zeros(shape, dtype=dtype, device=device)
+                    v = torch.zeros(shape, dtype=dtype, device=device) if g.need.values else k
+                    self.site_cache[i] = PagedSiteCache(gi, page_size, k, v)
             for i in self._slot_sites:
                 need = needs[i]
                 self.site_cache[i] = SlotSiteCache(torch.zeros((max_requests, *need.shape), dtype=need.dtype, device=device))

@@ -5,10 +5,13 @@ from .lfm2_moe import MODEL_TYPES as _LFM2_TYPES
 from .lfm2_moe import Lfm2MoeConfig
 from .registry import (REGISTRY, Architecture, architecture_of, read_model_config, register, resolve_model_folder,
                        spec_of, unregister)
+from .puripel import ARCHITECTURES as _PURIPEL_ARCHS
+from .puripel import MODEL_TYPES as _PURIPEL_TYPES
+from .puripel import PuripelConfig
 from .sifupel import ARCHITECTURES as _SIFUPEL_ARCHS
 from .sifupel import MODEL_TYPES as _SIFUPEL_TYPES
 from .sifupel import SifupelConfig
-from .spec import LayerSpec, ModelSpec, PartSpec, Site, plain_schedule
+from .spec import LayerSpec, ModelSpec, PartSpec, Site, StreamAdd, plain_schedule
 
 register(Architecture(name="lfm2_moe", architectures=_LFM2_ARCHS, model_types=_LFM2_TYPES,
                       read_config=Lfm2MoeConfig.from_dict))
@@ -16,6 +19,9 @@ register(Architecture(name="lfm2_moe", architectures=_LFM2_ARCHS, model_types=_L
 register(Architecture(name="sifupel", architectures=_SIFUPEL_ARCHS, model_types=_SIFUPEL_TYPES,
                       read_config=SifupelConfig.from_dict))
 
-__all__ = ["REGISTRY", "Architecture", "architecture_of", "read_model_config", "register", "unregister",
-           "resolve_model_folder", "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "Site", "plain_schedule",
+register(Architecture(name="puripel", architectures=_PURIPEL_ARCHS, model_types=_PURIPEL_TYPES,
+                      read_config=PuripelConfig.from_dict))
+
+__all__ = ["PuripelConfig", "REGISTRY", "Architecture", "architecture_of", "read_model_config", "register", "unregister",
+           "resolve_model_folder", "spec_of", "LayerSpec", "ModelSpec", "PartSpec", "Site", "StreamAdd", "plain_schedule",
            "Lfm2MoeConfig", "SifupelConfig"]

@@ -43,16 +43,28 @@ class LayerSpec:
     mixer: PartSpec
     feed_forward: PartSpec
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: PartSpec | None          # None: the layer has no feed-forward and no norm for one
     arrangement: str = "prenorm_residual"
+    mixer_post_norm: PartSpec | None = None            # arrangements that norm a branch's output as well
+    feed_forward_post_norm: PartSpec | None = None
+
+
+@dataclass(frozen=True)
+class StreamAdd:
+    """A stored vector that is added to every row of the residual stream: row `row` of the tensor `tensor` [rows, hidden]."""
+    tensor: str
+    row: int
+    rows: int
 
 
 @dataclass(frozen=True)
 class Site:
     """One entry of the run order: run `layer`'s weights; read and write the cache of site `cache_of`
-    (None: this site's own cache)."""
+    (None: this site's own cache). `add`: a vector added to the residual stream right before the site's layer runs (a
+    layer that is run several times in a row can be told which pass it is in this way)."""
     layer: int
     cache_of: int | None = None
+    add: StreamAdd | None = None
 
 
 @dataclass(frozen=True)

@@ -26,6 +26,11 @@ inline void tl_set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+// The constants of a gate form that has some (TL_ACT_CLAMPED_SWISH) travel beside its code: the caller sets them for its
+// thread (each library exports tl_set_gate_constants) and every gated launcher copies them into its kernel's arguments,
+// so a captured launch keeps the values it was captured with.
+inline thread_local float tl_gate_constants[2] = {0.f, 0.f};
+
 #define TL_REQUIRE(cond, ...)            \
   do {                                   \
     if (!(cond)) {                       \
@@ -149,7 +154,8 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 #define TL_ACT_RELU2 3       // max(x, 0)^2
 #define TL_ACT_IDENTITY 4    // gate * up
 #define TL_ACT_XIELU 5       // a0 z^2 + z / 2 for z > 0, a1 (exp(z) - 1 - z) + z / 2 else; a0, a1 travel beside the code
-#define TL_ACT_LAST 5
+#define TL_ACT_CLAMPED_SWISH 6   // a gate form of its own: g' = min(g, a0), u' = clamp(u, -a0, a0); g' sigmoid(a1 g') (u' + 1)
+#define TL_ACT_LAST 6
 
 __device__ __forceinline__ float gate_activation(float g, int act) {
   switch (act) {
@@ -165,6 +171,14 @@ __device__ __forceinline__ float activation(float z, int act, float a0, float a1
   return gate_activation(z, act);
 }
 __device__ __forceinline__ float gated(float g, float u, int act) { return gate_activation(g, act) * u; }
+// The same with the constants of a gate form that has some (`a0`, `a1`; TL_ACT_CLAMPED_SWISH: the limit and the slope).
+__device__ __forceinline__ float gated(float g, float u, int act, float a0, float a1) {
+  if (act == TL_ACT_CLAMPED_SWISH) {
+    const float gc = fminf(g, a0), uc = fminf(fmaxf(u, -a0), a0);
+    return gc / (1.f + expf(-a1 * gc)) * (uc + 1.f);
+  }
+  return gate_activation(g, act) * u;
+}
 
 // The current device's number of SMs (asked once a device; 148 on a B200), for grids sized to the GPU.
 inline int sm_count() {

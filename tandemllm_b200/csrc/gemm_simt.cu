@@ -29,6 +29,7 @@ struct GemmParams {
   const int* n_tiles;      // [1]
   const int* a_gather;     // [M] or nullptr: A row of sorted row i is a_gather[i] / a_div
   int a_div;
+  float ga0, ga1;          // the constants of a gate form that has some
   int swiglu;              // a gate activation TL_ACT_* (1: SiLU): W holds 2 N rows per group; C = act(A W[0:N]^T) * (A W[N:2N]^T)
 };
 
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(256) gemm_tiled_kernel(GemmParams p) {
       if (n >= p.N) continue;
       float v = acc[i][j];
       if constexpr (SWIGLU) {
-        v = gated(v, acc2[i][j], p.swiglu);
+        v = gated(v, acc2[i][j], p.swiglu, p.ga0, p.ga1);
       } else {
         if (p.bias) v += p.bias[n];
       }
@@ -294,6 +295,7 @@ extern "C" int tl_gemm_simt_grouped(const void* A, long long lda, const int* a_g
   p.w_group_stride = w_group_stride; p.M = n_sorted_rows; p.N = N; p.K = K;
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles;
   p.a_gather = a_gather; p.a_div = a_div; p.swiglu = swiglu;
+  p.ga0 = tl_gate_constants[0]; p.ga1 = tl_gate_constants[1];
   if (in_dtype == TL_FP32 && out_dtype == TL_FP32) launch<float, float>(p, max_tiles, stream);
   else if (in_dtype == TL_BF16 && out_dtype == TL_BF16) launch<bf16, bf16>(p, max_tiles, stream);
   else if (in_dtype == TL_BF16 && out_dtype == TL_FP32) launch<bf16, float>(p, max_tiles, stream);

@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
     long long ldw, long long rows_per_group, TOut* __restrict__ out, long long ldc, int N, int K,
     const int* __restrict__ tile_group, const int* __restrict__ tile_row0, const int* __restrict__ tile_rows,
     const int* __restrict__ n_tiles, const int* __restrict__ pair_group, int n_pairs, int n_groups,
-    int* __restrict__ status, int act, uint32_t zero) {
+    int* __restrict__ status, int act, float ga0, float ga1, uint32_t zero) {
   constexpr int W_TILES = SWIGLU ? 2 : 1;
   constexpr int UNROLL = SWIGLU ? 4 : 8;
   __shared__ float part[SKINNY_WARPS][W_TILES][16][8 + 1];
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(SKINNY_WARPS * 32) gemm_skinny_grouped_kernel(
 #pragma unroll
       for (int s = 0; s < SKINNY_WARPS; ++s) v[j] += part[s][j][row][m];
     }
-    const float r = SWIGLU ? gated(v[0], v[W_TILES - 1], act) : v[0];
+    const float r = SWIGLU ? gated(v[0], v[W_TILES - 1], act, ga0, ga1) : v[0];
     out[(long long)s_pair[m] * ldc + n0 + row] = from_f32<TOut>(r);
   }
 }
@@ -467,7 +467,7 @@ extern "C" int tl_gemm_skinny_grouped(const void* x, long long ldx, const int* r
 #define TL_GROUPED(SW_, T_)                                                                                              \
   return (int)launch_chained(gemm_skinny_grouped_kernel<SW_, T_>, grid, block, 0, stream, (const bf16*)x, ldx, row_index,  \
                              row_div, (const bf16*)w, ldw, rows_per_group, (T_*)out, ldc, N, K, tile_group, tile_row0,    \
-                             tile_rows, n_tiles, pair_group, n_pairs, n_groups, status, swiglu, 0u)
+                             tile_rows, n_tiles, pair_group, n_pairs, n_groups, status, swiglu, tl_gate_constants[0], tl_gate_constants[1], 0u)
   if (swiglu) {
     if (out_dtype == TL_FP32) TL_GROUPED(true, float);
     TL_GROUPED(true, bf16);

@@ -5,8 +5,13 @@
 // (engine/models/lfm2_moe/ref.py:185-197, engine/models/lfm2_moe/kernels.py:265-287 of the reference; the softmax
 // scoring is what its other routed families use, engine/models/flashnext/ref.py:479-487)
 //
-// The launchers' `normalize` argument carries both choices: bit 0 = divide the chosen weights by their sum,
-// bits 1.. = the scoring function (TL_SCORE_SIGMOID 0, TL_SCORE_SOFTMAX 1).
+// The launchers' `normalize` argument carries the router's choices: bit 0 = divide the chosen weights by their sum,
+// bits 1..3 = the scoring function (TL_SCORE_SIGMOID 0, TL_SCORE_SOFTMAX 1), bits 4..9 = the number of expert groups
+// (0: the choice is free) and bits 10..15 = how many of them are kept.
+//
+// Group-limited choice: the experts form `groups` equal groups of neighbours; a group's score is the sum of its two
+// largest choice scores (score + bias); only the experts of the `keep` best groups (ties to the lower group) can be
+// chosen: the others' choice scores count as minus infinity.
 #pragma once
 
 #include "common.cuh"
@@ -16,6 +21,10 @@ namespace tl {
 #define TL_SCORE_SIGMOID 0
 #define TL_SCORE_SOFTMAX 1
 #define TL_SCORE_LAST 1
+#define TL_ROUTE_SCORING(flags) (((flags) >> 1) & 7)
+#define TL_ROUTE_GROUPS(flags) (((flags) >> 4) & 63)
+#define TL_ROUTE_KEEP(flags) (((flags) >> 10) & 63)
+#define TL_ROUTE_MAX_GROUPS 32
 
 constexpr int MAX_EXPERTS = 1024;
 constexpr int MAX_TOP_K = 32;
@@ -26,7 +35,8 @@ template <int PER>
 __device__ __forceinline__ void warp_route_sized(const float* lg, const float* __restrict__ bias, int E, int k,
                                                  int normalize, float floor_, float scale, int* ids, float* wts) {
   const int lane = threadIdx.x & 31;
-  const int scoring = normalize >> 1;
+  const int scoring = TL_ROUTE_SCORING(normalize);
+  const int n_groups = TL_ROUTE_GROUPS(normalize), keep_groups = TL_ROUTE_KEEP(normalize);
   normalize &= 1;
   float score[PER], choice[PER];
   float top = -INFINITY, denom = 1.f;
@@ -52,6 +62,43 @@ __device__ __forceinline__ void warp_route_sized(const float* lg, const float* _
     } else {
       score[t] = 0.f;
       choice[t] = -INFINITY;
+    }
+  }
+  if (n_groups > 1 && keep_groups < n_groups) {
+    // lane g ends up with group g's score (at most 32 groups); every lane learns which groups are kept
+    const int per = E / n_groups;
+    float mine = -INFINITY;
+    for (int g = 0; g < n_groups; ++g) {
+      float a = -INFINITY, b = -INFINITY;           // the two largest choice scores of group g seen by this lane
+#pragma unroll
+      for (int t = 0; t < PER; ++t) {
+        const int e = lane + 32 * t;
+        if (e < E && e / per == g) {
+          const float c = choice[t];
+          if (c > a) { b = a; a = c; }
+          else if (c > b) b = c;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, a, o), ob = __shfl_xor_sync(0xffffffffu, b, o);
+        const float hi = fmaxf(a, oa), lo = fminf(a, oa);
+        b = fmaxf(lo, fmaxf(b, ob));
+        a = hi;
+      }
+      const float gs = b == -INFINITY ? a : a + b;
+      if (lane == g) mine = gs;
+    }
+    int rank = 0;
+    for (int g = 0; g < n_groups; ++g) {
+      const float other = __shfl_sync(0xffffffffu, mine, g);
+      rank += (other > mine) || (other == mine && g < lane);
+    }
+    const unsigned kept = __ballot_sync(0xffffffffu, lane < n_groups && rank < keep_groups);
+#pragma unroll
+    for (int t = 0; t < PER; ++t) {
+      const int e = lane + 32 * t;
+      if (e < E && !((kept >> (e / per)) & 1u)) choice[t] = -INFINITY;
     }
   }
   float sum = 0.f, my_w = 0.f;

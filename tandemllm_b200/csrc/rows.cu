@@ -9,6 +9,13 @@
 
 extern "C" const char* tl_last_error() { return tl_error_text; }
 
+// The constants that the gated launches of this thread pass beside their activation code from now on.
+extern "C" int tl_set_gate_constants(float a0, float a1) {
+  tl_gate_constants[0] = a0;
+  tl_gate_constants[1] = a1;
+  return 0;
+}
+
 extern "C" const char* tl_cuda_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 
 namespace tl {
@@ -452,7 +459,8 @@ __global__ void __launch_bounds__(512, ONE_ROW ? 1 : (ROUTE_PER <= 4 ? 2 : 1)) a
 
 // out[r, i] = act(gate_up[r, i]) * gate_up[r, inter + i]
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows, int inter, int act) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows, int inter, int act,
+                                float ga0, float ga1) {
   chain_next();
   chain_wait();
   const long long n = rows * inter;
@@ -461,7 +469,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const int c = (int)(i - r * inter);
     const float g = to_f32(gate_up[r * 2 * inter + c]);
     const float u = to_f32(gate_up[r * 2 * inter + inter + c]);
-    out[i] = from_f32<T>(gated(g, u, act));
+    out[i] = from_f32<T>(gated(g, u, act, ga0, ga1));
   }
 }
 
@@ -522,7 +530,7 @@ extern "C" int tl_add_rmsnorm(float* residual, const float* delta, int parts, lo
     TL_REQUIRE(E > 0 && E <= MAX_EXPERTS, "router: %d experts; up to %d are implemented", E, MAX_EXPERTS);
     TL_REQUIRE(route_k > 0 && route_k <= E && route_k <= MAX_TOP_K && route_ids && route_wts,
                "router: top-%d of %d experts; up to top-%d is implemented", route_k, E, MAX_TOP_K);
-    TL_REQUIRE(normalize >= 0 && (normalize >> 1) <= TL_SCORE_LAST, "router: scoring function %d is not one of 0..%d",
+    TL_REQUIRE(normalize >= 0 && TL_ROUTE_SCORING(normalize) <= TL_SCORE_LAST, "router: scoring function %d is not one of 0..%d",
                normalize >> 1, TL_SCORE_LAST);
   }
   // prompts: several rows a block (eight beside a router, whose weights are then read once for eight rows)
@@ -593,9 +601,9 @@ extern "C" int tl_gated_mul(const void* gate_up, void* out, int rows, int inter,
   cudaError_t e;
   if (dtype == TL_FP32)
     e = launch_chained(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gate_up, (float*)out,
-                       (long long)rows, inter, act);
+                       (long long)rows, inter, act, tl_gate_constants[0], tl_gate_constants[1]);
   else
     e = launch_chained(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)gate_up, (bf16*)out,
-                       (long long)rows, inter, act);
+                       (long long)rows, inter, act, tl_gate_constants[0], tl_gate_constants[1]);
   return (int)e;
 }

@@ -47,6 +47,7 @@ struct TcParams {
   const int* row_index;       // grouped, swapped: token row of sorted position i is row_index[i] / row_div of X (or nullptr:
   int row_div;                // X is already in sorted order)
   int act;                    // the gate's activation of a gated product (TL_ACT_*), 0 for a plain one
+  float ga0, ga1;             // the constants of a gate form that has some
   int skip_kb;                // -1; a test sets the k-block whose copies the producer leaves out, so that a wait runs out
   int* status;
 };
@@ -311,7 +312,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
             for (int j = 0; j < 16; ++j) {
               const int t = c0 + j;
               if (t < tok_rows) {
-                const float r = SWIGLU ? gated(v[j], u[j], p.act) : v[j] + b;
+                const float r = SWIGLU ? gated(v[j], u[j], p.act, p.ga0, p.ga1) : v[j] + b;
                 if (p.partial) p.partial[((long long)blockIdx.z * p.M + tok0 + t) * p.N + n] = r;
                 else store_out<TOut>(C + (long long)(tok0 + t) * p.ldc + n, r);
               }
@@ -325,7 +326,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const int n = n0 + c0 + j;
-              r[j] = SWIGLU ? gated(v[j], u[j], p.act) : v[j] + ((p.bias && n < p.N) ? p.bias[n] : 0.f);
+              r[j] = SWIGLU ? gated(v[j], u[j], p.act, p.ga0, p.ga1) : v[j] + ((p.bias && n < p.N) ? p.bias[n] : 0.f);
             }
             // 16 consecutive outputs of one row: 16-byte stores when they are all there and aligned
             const bool whole = n0 + c0 + 16 <= p.N && (((uintptr_t)(row + n0 + c0)) & 15) == 0;
@@ -534,7 +535,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int col = n0 + c0 + j;
-            r[j] = SWIGLU ? gated(v[j], u[j], p.act) : v[j] + ((p.bias && col < p.N) ? p.bias[col] : 0.f);
+            r[j] = SWIGLU ? gated(v[j], u[j], p.act, p.ga0, p.ga1) : v[j] + ((p.bias && col < p.N) ? p.bias[col] : 0.f);
           }
           const bool whole = n0 + c0 + 16 <= p.N && (((uintptr_t)(row + n0 + c0)) & 15) == 0;
           if (whole) {
@@ -654,6 +655,13 @@ using namespace tl;
 
 extern "C" const char* tl_tc_last_error() { return tl_error_text; }
 
+// The constants that the gated launches of this thread pass beside their activation code from now on.
+extern "C" int tl_tc_set_gate_constants(float a0, float a1) {
+  tl_gate_constants[0] = a0;
+  tl_gate_constants[1] = a1;
+  return 0;
+}
+
 // The token-tile height the grouped kernel wants for a given orientation (the MoE plan is built with it).
 extern "C" int tl_tc_token_tile(int swap, int bn) { return swap ? bn : TILE_M; }
 
@@ -696,6 +704,7 @@ extern "C" int tl_gemm_tc(const void* X, long long ldx, long long x_rows, const 
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles; p.status = status;
   p.row_index = row_index; p.row_div = row_index ? row_div : 1;
   p.act = swiglu;
+  p.ga0 = tl_gate_constants[0]; p.ga1 = tl_gate_constants[1];
   p.skip_kb = skip_kb_for_test();
   const int tok_tile = swap ? bn : TILE_M, n_tile = swap ? TILE_M : bn;
   // one CTA layer a split, also where rounding leaves the last splits without k-blocks: they write zeros

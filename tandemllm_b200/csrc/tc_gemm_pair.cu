@@ -50,6 +50,7 @@ struct Params {
   int act;                    // the gate's activation (TL_ACT_*), 0 for a plain product
   int unary;                  // plain product: an activation (TL_ACT_*) applied to every output (after the bias), 0 for none
   float a0, a1;               // that activation's constants
+  float ga0, ga1;             // the constants of a gate form that has some
   int skip_kb;                // -1; a test sets the k-block (counted over a cluster's tiles) whose copies both producers leave out
   int splits;                 // plain, ungrouped: work items a tile, each a run of k-blocks with a 32-bit partial result of its own
   int kb_per_split;           // k-blocks a run (every run holds at least one)
@@ -371,7 +372,7 @@ __global__ void __launch_bounds__(Smem<GATED, PER_SM>::THREADS, PER_SM) gemm_tc_
             for (int j = 0; j < 16; ++j) v[j] = __fdividef(v[j], 1.f + __expf(-v[j])) * u[j];
           } else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = gated(v[j], u[j], p.act);
+            for (int j = 0; j < 16; ++j) v[j] = gated(v[j], u[j], p.act, p.ga0, p.ga1);
           }
         } else {
 #pragma unroll
@@ -555,6 +556,7 @@ static int pair_product(const void* X, long long ldx, long long x_rows, const vo
   p.tile_group = tile_group; p.tile_row0 = tile_row0; p.tile_rows = tile_rows; p.n_tiles = n_tiles;
   p.plan_rows = plan_rows;
   p.act = gated; p.status = status;
+  p.ga0 = tl_gate_constants[0]; p.ga1 = tl_gate_constants[1];
   p.unary = unary; p.a0 = a0; p.a1 = a1;
   p.skip_kb = pair::skip_kb_for_test();
   p.splits = splits; p.kb_per_split = kb_per_split; p.part_stride = splits > 1 ? (long long)M * ldc : 0;

@@ -18,7 +18,7 @@ FP32, BF16 = 0, 1
 TL_BAD_ARGUMENT = 100001
 # the gate activations of gated products (TL_ACT_* of csrc/common.cuh) and the router's scoring functions (TL_SCORE_*
 # of csrc/route.cuh), by the names a part's spec gives them
-ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5}
+ACTIVATIONS = {"silu": 1, "gelu": 2, "relu2": 3, "identity": 4, "xielu": 5, "clamped_swish": 6}
 SCORINGS = {"sigmoid": 0, "softmax": 1}
 
 
@@ -28,11 +28,25 @@ def activation_code(name: str) -> int:
     return ACTIVATIONS[name]
 
 
-def route_flags(normalize: bool, scoring: str = "sigmoid") -> int:
-    """The routers' `normalize` argument: bit 0 = divide the chosen weights by their sum, bits 1.. = the scoring function."""
+def route_flags(normalize: bool, scoring: str = "sigmoid", groups: tuple[int, int] | None = None) -> int:
+    """The routers' `normalize` argument: bit 0 = divide the chosen weights by their sum, bits 1..3 = the scoring function,
+    bits 4..9 = the number of expert groups and bits 10..15 = how many of them are kept (`groups` = (count, keep); None: the
+    choice is free)."""
     if scoring not in SCORINGS:
         raise KernelError(f"router scoring function {scoring!r}: one of {', '.join(SCORINGS)}")
-    return int(bool(normalize)) | (SCORINGS[scoring] << 1)
+    count, keep = groups or (0, 0)
+    if groups is not None and not (1 <= keep <= count <= 32):
+        raise KernelError(f"router groups: {keep} of {count} kept; 1 <= keep <= count <= 32")
+    return int(bool(normalize)) | (SCORINGS[scoring] << 1) | (count << 4) | (keep << 10)
+
+
+def gate_constants(a0: float, a1: float) -> None:
+    """The constants of a gate form that has some (`clamped_swish`: the limit and the slope) for the gated launches this
+    thread makes from now on, in every loaded library."""
+    core().tl_set_gate_constants(float(a0), float(a1))
+    from . import tensorcore
+    if tensorcore.loaded():
+        tensorcore.lib().tl_tc_set_gate_constants(float(a0), float(a1))
 
 
 class KernelError(RuntimeError):
@@ -91,6 +105,24 @@ _SIGNATURES = {
                     c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p],
     "tl_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
+    "tl_add_normed": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p,
+                      c_int, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tl_add_vector": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "tl_causal_conv_act": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_longlong, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_conv_state": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "tl_ssm_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
+                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_gated_group_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "tl_latent_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                          c_void_p],
+    "tl_rmsnorm_rows": [c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
+    "tl_head_linear": [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int, c_int, c_int,
+                       c_int, c_int, c_void_p],
+    "tl_attention_latent": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "tl_set_gate_constants": [c_float, c_float],
     "tl_graph_capture_begin": [c_void_p],
     "tl_graph_capture_end": [c_void_p, c_void_p, c_void_p],
     "tl_graph_launch": [c_void_p, c_void_p],
@@ -205,9 +237,23 @@ class ExpertRows:
         return out
 
 
+class GatedSum:
+    """A branch output in three pieces: dense [rows, hidden] (a tensor or `PartialSums`) times sigmoid(gate[r]) (float32
+    [rows, 1] logits; None: no gate), plus the weighed rows of `experts` (`ExpertRows` or None)."""
+
+    def __init__(self, dense, gate: torch.Tensor | None, experts: "ExpertRows | None"):
+        self.dense, self.gate, self.experts = dense, gate, experts
+
+    def materialize(self) -> torch.Tensor:
+        total = materialize(self.dense).float()
+        if self.gate is not None:
+            total = total * torch.sigmoid(self.gate.view(-1, 1))
+        return total if self.experts is None else total + self.experts.materialize()
+
+
 def materialize(branch):
     """A branch output as a plain tensor, whatever form a part returned it in."""
-    return branch.materialize() if isinstance(branch, (PartialSums, ExpertRows)) else branch
+    return branch.materialize() if isinstance(branch, (PartialSums, ExpertRows, GatedSum)) else branch
 
 
 def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -231,6 +277,7 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
         if delta.parts > 1:
             eparts, estride = delta.parts, delta.rows.shape[1] * delta.rows.shape[2]
     elif delta is not None:
+        delta = materialize(delta)
         _need(delta, torch.float32, "delta")
         dense, parts = delta.data_ptr(), 1
     hidden = residual.shape[-1]
@@ -243,7 +290,7 @@ def add_rmsnorm(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float,
         ptr(weight),
         ptr(out), ptr(out32), ptr(gather), n_out, hidden, float(eps), dtype_code(out.dtype), ptr(r.get("weight")),
         ptr(r.get("bias")), r["weight"].shape[0] if route else 0, int(r.get("k", 0)),
-        route_flags(r.get("normalize", 0), r.get("scoring", "sigmoid")),
+        route_flags(r.get("normalize", 0), r.get("scoring", "sigmoid"), r.get("groups")),
         float(r.get("floor", 0.0)), float(r.get("scale", 1.0)), ptr(r.get("ids")), ptr(r.get("wts")), stream()),
         "add_rmsnorm")
     return out
@@ -286,6 +333,145 @@ def activation(x: torch.Tensor, out: torch.Tensor, act: int, a0: float = 0.0, a1
     _need(x, out.dtype, "x"); _need(out, None, "out")
     check(core().tl_activation(ptr(x), ptr(out), x.numel(), int(act), float(a0), float(a1), dtype_code(out.dtype), stream()),
           "activation")
+    return out
+
+
+def add_normed(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float, gate: torch.Tensor | None = None,
+               experts: "ExpertRows | None" = None, then: tuple | None = None) -> torch.Tensor | None:
+    """The norm behind a branch, fused with the residual add: d = delta (None, a float32 tensor or `PartialSums`), times
+    sigmoid(gate[r]) where `gate` (float32 [rows] logits) is given, plus the weighed rows of `experts`;
+    residual += weight * d / rms(d). `then` = (next norm's weight, its eps, out, gather or None): the kernel also writes
+    the next norm's rows of the new residual into `out` (with `gather`, only of those rows, whose residual then stays as it
+    was); returns `out` or None."""
+    _need(residual, torch.float32, "residual"); _need(weight, torch.float32, "norm weight")
+    dense, parts, stride = None, 0, 0
+    if isinstance(delta, PartialSums):
+        if delta.dtype is not None:
+            delta = delta.materialize().float()
+        else:
+            dense, parts, stride = delta.data.data_ptr(), delta.parts, delta.rows * delta.hidden
+    if isinstance(delta, ExpertRows):
+        experts, delta = delta, None
+    if isinstance(delta, torch.Tensor):
+        _need(delta, torch.float32, "delta")
+        dense, parts = delta.data_ptr(), 1
+    rows_ptr = pos = ids = wts = None
+    top_k, eparts, estride = 0, 1, 0
+    if experts is not None:
+        rows_ptr, pos, ids, wts, top_k = experts.rows, experts.pos_of_pair, experts.ids, experts.wts, experts.ids.shape[1]
+        if experts.parts > 1:
+            eparts, estride = experts.parts, experts.rows.shape[1] * experts.rows.shape[2]
+    if gate is not None:
+        _need(gate, torch.float32, "gate logits")
+    hidden = residual.shape[-1]
+    pre_w, pre_eps, out, gather = then if then is not None else (None, 0.0, None, None)
+    rows = residual.shape[0] if gather is None else out.shape[0]
+    check(core().tl_add_normed(ptr(residual), dense, parts, stride, ptr(gate), ptr(rows_ptr), eparts, estride, ptr(pos), ptr(ids),
+                               ptr(wts), top_k, ptr(weight), float(eps), ptr(pre_w), float(pre_eps), ptr(out), ptr(gather),
+                               rows, hidden, dtype_code(out.dtype) if out is not None else FP32, stream()), "add_normed")
+    return out
+
+
+def add_vector(residual: torch.Tensor, vec: torch.Tensor) -> None:
+    """residual[r, :] += vec for every row."""
+    _need(residual, torch.float32, "residual"); _need(vec, torch.float32, "vector")
+    if vec.numel() != residual.shape[-1]:
+        raise KernelError(f"a vector of {vec.numel()} for rows of {residual.shape[-1]}")
+    check(core().tl_add_vector(ptr(residual), ptr(vec), residual.shape[0], residual.shape[1], stream()), "add_vector")
+
+
+# ------------------------------------------------------------------------------------------ state-space mixer
+CONV_ACTIVATIONS = {"none": 0, "silu": 1}
+
+
+def causal_conv_act(x: torch.Tensor, channels: int, taps, bias, state: torch.Tensor, state_slot, req_of_row, row_start,
+                    out: torch.Tensor, act: str = "silu") -> torch.Tensor:
+    """out[r, c] = act(bias[c] + sum_k taps[c, k] x[r - (K - 1) + k, c]) over each request's own rows; inputs before the
+    step come from the request's slot of `state` (float32 [slots, floats]; the first (K - 1) * channels floats of a slot
+    are its last K - 1 inputs, oldest first). `x` is a float32 view whose first `channels` columns are convolved."""
+    _need(taps, torch.float32, "taps"); _need(state, torch.float32, "state"); _need(out, torch.float32, "out")
+    if x.dtype != torch.float32 or x.stride(-1) != 1:
+        raise KernelError("causal conv: float32 rows with unit stride")
+    check(core().tl_causal_conv_act(ptr(x), x.stride(0), ptr(taps), ptr(bias), ptr(state), state.stride(0), ptr(state_slot),
+                                    ptr(req_of_row), ptr(row_start), ptr(out), out.stride(0), x.shape[0], channels,
+                                    taps.shape[1], CONV_ACTIVATIONS[act], stream()), "causal_conv_act")
+    return out
+
+
+def conv_state(x: torch.Tensor, channels: int, taps: int, state: torch.Tensor, state_slot, row_start, requests: int) -> None:
+    """After a step: each request's slot holds its last `taps - 1` inputs (rows of `x`, or what the slot held)."""
+    check(core().tl_conv_state(ptr(x), x.stride(0), ptr(state), state.stride(0), ptr(state_slot), ptr(row_start), requests,
+                               channels, taps, stream()), "conv_state", kernels=1 if taps > 1 else 0)
+
+
+def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, state: torch.Tensor, state_offset: int, state_slot,
+             row_start, requests: int, y: torch.Tensor, heads: int, cols: int, n_state: int, groups: int,
+             write_state: bool = True) -> torch.Tensor:
+    """The selective state-space recurrence of csrc/ssm.cu over each request's rows. `xbc` float32 [rows, H P + 2 G N];
+    `dt` a float32 view [rows, H] of the raw step sizes; a slot's recurrent state [H, P, N] begins `state_offset` floats
+    into its row of `state`; `y` float32 [rows, H P]."""
+    _need(xbc, torch.float32, "xbc"); _need(y, torch.float32, "y"); _need(state, torch.float32, "state")
+    if dt.dtype != torch.float32 or dt.stride(-1) != 1:
+        raise KernelError("ssm scan: float32 step sizes with unit stride")
+    check(core().tl_ssm_scan(ptr(xbc), xbc.stride(0), ptr(dt), dt.stride(0), ptr(dt_bias), ptr(a_log), ptr(d_skip),
+                             state.data_ptr() + 4 * state_offset, state.stride(0), ptr(state_slot), ptr(row_start), ptr(y),
+                             requests, heads, cols, n_state, groups, int(write_state), stream()), "ssm_scan")
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight, eps: float, groups: int, out: torch.Tensor) -> torch.Tensor:
+    """out = weight * v / rms(v) in `groups` equal parts of a row, v = y * silu(z); `z` a float32 view [rows, inner]."""
+    _need(y, torch.float32, "y"); _need(weight, torch.float32, "norm weight"); _need(out, None, "out")
+    if z.dtype != torch.float32 or z.stride(-1) != 1:
+        raise KernelError("gated group norm: a float32 gate with unit stride")
+    check(core().tl_gated_group_norm(ptr(y), ptr(z), z.stride(0), ptr(weight), float(eps), ptr(out), y.shape[0], y.shape[1],
+                                     groups, dtype_code(out.dtype), stream()), "gated_group_norm")
+    return out
+
+
+# ------------------------------------------------------------------------------------------ latent attention
+def latent_prepare(q, kv, c_weight, eps, inv_freq, rot_dims, positions, req_of_row, table, page_size, cache, q_out,
+                   heads: int, dim: int, latent: int, rot_dim: int, status) -> None:
+    """Writes the normed latent and the rotated shared key part of every row into its page, and every head's rotated query
+    part into `q_out` (float32 [rows, heads, latent + rot_dim]) behind the place of its absorbed part (csrc/attention_latent.cu)."""
+    _need(q, cache.dtype, "q"); _need(q_out, torch.float32, "q'")
+    if kv.dtype != cache.dtype or kv.stride(-1) != 1:
+        raise KernelError("latent prepare: the latent's rows in the cache's type with unit stride")
+    check(core().tl_latent_prepare(ptr(q), q.stride(0), ptr(kv), kv.stride(0), ptr(c_weight), float(eps), ptr(inv_freq),
+                                   int(rot_dims), ptr(positions), ptr(req_of_row), ptr(table), table.shape[1], int(page_size),
+                                   cache.shape[0], ptr(cache), ptr(q_out), q.shape[0], heads, dim, latent, rot_dim,
+                                   dtype_code(q.dtype), ptr(status), stream()), "latent_prepare")
+
+
+def rmsnorm_rows(x: torch.Tensor, n: int, weight: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[r, :n] = weight * x[r, :n] / rms(x[r, :n]): a plain RMS norm over the first n columns of strided rows, 32-bit
+    inside, rows in and out in the compute dtype."""
+    _need(weight, torch.float32, "norm weight")
+    if x.dtype != out.dtype or x.stride(-1) != 1 or out.stride(-1) != 1:
+        raise KernelError("rmsnorm rows: rows in and out of one type with unit stride")
+    check(core().tl_rmsnorm_rows(ptr(x), x.stride(0), ptr(weight), float(eps), ptr(out), out.stride(0), x.shape[0], int(n),
+                                 dtype_code(x.dtype), stream()), "rmsnorm_rows")
+    return out
+
+
+def head_linear(a: torch.Tensor, ld_a: int, a_head: int, w: torch.Tensor, out: torch.Tensor, ld_out: int, out_head: int,
+                rows: int) -> torch.Tensor:
+    """out[r, h, n] = sum_k a[r, h, k] w[h, n, k] with w [heads, N, K]; `a` and `out` addressed by a row stride and a head
+    stride (elements)."""
+    _need(w, a.dtype, "head weights")
+    H, N, K = w.shape
+    check(core().tl_head_linear(ptr(a), int(ld_a), int(a_head), ptr(w), ptr(out), int(ld_out), int(out_head), rows, H, N, K,
+                                dtype_code(a.dtype), dtype_code(out.dtype), stream()), "head_linear")
+    return out
+
+
+def attention_latent(q, cache, table, page_size, req_of_row, positions, scale, window, out, latent: int, status) -> torch.Tensor:
+    """out[r, h, :latent] = softmax over the visible keys of scale * q[r, h] . key, applied to the keys' latent parts."""
+    _need(q, torch.float32, "q'"); _need(out, cache.dtype, "out")
+    rows, H, Dk = q.shape
+    check(core().tl_attention_latent(ptr(q), ptr(cache), ptr(table), table.shape[1], int(page_size), cache.shape[0],
+                                     ptr(req_of_row), ptr(positions), float(scale), int(window or 0), ptr(out), rows, H, latent,
+                                     Dk, dtype_code(cache.dtype), ptr(status), stream()), "attention_latent")
     return out
 
 
@@ -478,10 +664,11 @@ def attention_headmix(q, k_cache, v_cache, block_table, page_size, req_of_row, p
 
 
 # ------------------------------------------------------------------------------------------ experts
-def router_topk(logits, bias, k: int, normalize: bool, floor: float, scale: float, ids, wts, scoring: str = "sigmoid") -> None:
+def router_topk(logits, bias, k: int, normalize: bool, floor: float, scale: float, ids, wts, scoring: str = "sigmoid",
+                groups: tuple[int, int] | None = None) -> None:
     _need(logits, torch.float32, "router logits"); _need(ids, torch.int32, "ids"); _need(wts, torch.float32, "weights")
     rows, E = logits.shape
-    check(core().tl_router_topk(ptr(logits), logits.stride(0), ptr(bias), rows, E, k, route_flags(normalize, scoring), float(floor),
+    check(core().tl_router_topk(ptr(logits), logits.stride(0), ptr(bias), rows, E, k, route_flags(normalize, scoring, groups), float(floor),
                                 float(scale), ptr(ids), ptr(wts), stream()), "router_topk")
 
 

@@ -55,6 +55,11 @@ PAIR_HALF_ROWS = 64             # rows an expert (on average) up to which the ex
 _lib = None
 
 
+def loaded() -> bool:
+    """Whether the tensor-core library is in use in this process (a 32-bit run never loads it)."""
+    return _lib is not None
+
+
 def lib():
     global _lib
     if _lib is None:
@@ -78,6 +83,8 @@ def lib():
         l.tl_tc_token_tile.argtypes = [c_int, c_int]
         l.tl_tc_token_tile.restype = c_int
         l.tl_tc_last_error.restype = ctypes.c_char_p
+        l.tl_tc_set_gate_constants.argtypes = [ctypes.c_float, ctypes.c_float]
+        l.tl_tc_set_gate_constants.restype = c_int
         l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
                                              c_void_p, ctypes.c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_void_p, c_void_p]

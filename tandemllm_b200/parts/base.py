@@ -22,6 +22,8 @@ Interfaces (duck-typed; the base classes below document them and hold the shared
                   beyond the rounded rows (the unrounded rows, a router run inside the norm kernel) stays between the
                   two of them; `Part.forward_from` is the plain form, which an arrangement may rely on
   Arrangement     run(layer, residual, pending, step, cache, writes_cache) -> pending  (the not-yet-added branch output)
+                  An arrangement that norms a branch's output too reads `layer.mixer_post_norm` and
+                  `layer.feed_forward_post_norm` (norms with `add_normed(residual, delta, ...)`: residual += norm(delta)).
 
 A branch output is what a mixer or feed-forward adds to the residual stream: a float32 tensor [R, hidden], or one of
 the deferred forms of `kernels.ops` (`PartialSums`, `ExpertRows`) that the next norm kernel adds itself;
@@ -120,6 +122,7 @@ class PagedNeed:
     kv_heads: int
     head_dim: int
     window: int | None = None
+    values: bool = True         # False: nothing is stored beside the keys (the site's `v` is its `k`)
 
 
 @dataclass(frozen=True)

@@ -24,8 +24,16 @@ import torch
 
 from ..kernels import ops
 from ..weights.loader import TensorSpec
-from .base import Part, register_part
+from .base import FEED_FORWARDS, Part, register_part
 from .linear import linear
+
+def gate_constants_of(spec):
+    """The constants of a gate form that has some, from a part's spec: `clamped_swish` reads `gate_limit` and `gate_slope`
+    (g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' sigmoid(slope g') (u' + 1)); None for the others."""
+    if spec.get("activation", "silu") != "clamped_swish":
+        return None
+    return float(spec["gate_limit"]), float(spec.get("gate_slope", 1.702))
+
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(Part):
@@ -35,22 +43,27 @@ class SwiGLU(Part):
         super().__init__(spec, prefix, hidden_size)
         self.inter = int(spec["intermediate_size"])
         self.act = ops.activation_code(spec.get("activation", "silu"))
+        self.gate_constants = gate_constants_of(spec)
+        self.suffix = str(spec.get("weight_suffix", ".weight"))
         self.n = {k: prefix + v for k, v in spec["names"].items()}
 
     def weight_specs(self, present=None):
-        H, I = self.hidden_size, self.inter
-        return [TensorSpec(self.n["gate"] + ".weight", (I, H)), TensorSpec(self.n["up"] + ".weight", (I, H)),
-                TensorSpec(self.n["down"] + ".weight", (H, I))]
+        H, I, sfx = self.hidden_size, self.inter, self.suffix
+        return [TensorSpec(self.n["gate"] + sfx, (I, H)), TensorSpec(self.n["up"] + sfx, (I, H)),
+                TensorSpec(self.n["down"] + sfx, (H, I))]
 
     def bind(self, read, runtime):
         self.runtime = runtime
-        self.w_gate_up = torch.cat([runtime.matrix(read(self.n["gate"] + ".weight")),
-                                    runtime.matrix(read(self.n["up"] + ".weight"))]).contiguous()
-        self.w_down = runtime.matrix(read(self.n["down"] + ".weight"))
+        sfx = self.suffix
+        self.w_gate_up = torch.cat([runtime.matrix(read(self.n["gate"] + sfx)),
+                                    runtime.matrix(read(self.n["up"] + sfx))]).contiguous()
+        self.w_down = runtime.matrix(read(self.n["down"] + sfx))
 
     def forward(self, x, step):
         act = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
         tc = self.runtime.tensorcore
+        if self.gate_constants is not None:
+            ops.gate_constants(*self.gate_constants)
         if tc is None or not tc.gated(x, self.w_gate_up, act, self.act):      # prompts: gate, up and act(gate) * up in one kernel
             gu = linear(self.runtime, x, self.w_gate_up)
             ops.gated_mul(gu, act, self.act)
@@ -104,6 +117,7 @@ class DenseActivation(Part):
 class NoFeedForward(Part):
     """A layer without a feed-forward: the mixer's output goes on, unadded, to the next layer's first norm."""
     graph_safe = True
+    absent = True
 
     def forward(self, x, step):
         return None
@@ -126,8 +140,14 @@ class SigmoidTopKExperts(Part):
         self.scale = float(spec.get("scale", 1.0))
         self.norm_floor = float(spec.get("norm_floor", 1e-6))
         self.scoring = str(spec.get("scoring", "sigmoid"))
-        ops.route_flags(self.normalize, self.scoring)          # an unknown scoring function is refused here
+        self.groups = tuple(int(v) for v in spec["groups"]) if spec.get("groups") else None     # (count, how many are kept)
+        if self.groups is not None and self.num_experts % self.groups[0]:
+            raise ValueError(f"{self.num_experts} experts do not fall into {self.groups[0]} equal groups")
+        ops.route_flags(self.normalize, self.scoring, self.groups)      # an unknown scoring function is refused here
         self.act = ops.activation_code(spec.get("activation", "silu"))
+        self.gate_constants = gate_constants_of(spec)
+        self.suffix = str(spec.get("weight_suffix", ".weight"))
+        self.sep = str(spec.get("expert_separator", "."))       # between the experts' common name and an expert's number
         if not 0 < self.top_k <= self.num_experts:
             raise ValueError(f"top-{self.top_k} of {self.num_experts} experts")
         if self.num_experts > 1024 or self.top_k > 32:
@@ -144,7 +164,7 @@ class SigmoidTopKExperts(Part):
 
     def weight_specs(self, present=None):
         H, I, E = self.hidden_size, self.inter, self.num_experts
-        out = [TensorSpec(self.prefix + self.n["router"] + ".weight", (E, H))]
+        out = [TensorSpec(self.prefix + self.n["router"] + self.suffix, (E, H))]
         if self.use_bias:
             out.append(TensorSpec(self.prefix + self.n["bias"], (E,), "vector", "bias"))
         self.stacked = self._stacked(present)
@@ -152,16 +172,18 @@ class SigmoidTopKExperts(Part):
             out += [TensorSpec(self.base + ".gate_up_proj", (E, 2 * I, H)), TensorSpec(self.base + ".down_proj", (E, H, I))]
         else:
             for e in range(E):
-                out += [TensorSpec(f"{self.base}.{e}.{self.n['gate']}.weight", (I, H)),
-                        TensorSpec(f"{self.base}.{e}.{self.n['up']}.weight", (I, H)),
-                        TensorSpec(f"{self.base}.{e}.{self.n['down']}.weight", (H, I))]
+                out += [TensorSpec(self._expert(e, "gate"), (I, H)), TensorSpec(self._expert(e, "up"), (I, H)),
+                        TensorSpec(self._expert(e, "down"), (H, I))]
         return out
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.base}{self.sep}{e}.{self.n[which]}{self.suffix}"
 
     def bind(self, read, runtime):
         self.runtime = runtime
         H, I, E = self.hidden_size, self.inter, self.num_experts
         # the router's product is 32-bit in both precisions: its weights are kept in 32-bit (E x H is small)
-        self.w_router = runtime.vector(read(self.prefix + self.n["router"] + ".weight"))
+        self.w_router = runtime.vector(read(self.prefix + self.n["router"] + self.suffix))
         self.expert_bias = runtime.vector(read(self.prefix + self.n["bias"])) if self.use_bias else None
         if self.stacked:
             self.w_gate_up = runtime.matrix(read(self.base + ".gate_up_proj"))
@@ -170,9 +192,9 @@ class SigmoidTopKExperts(Part):
             self.w_gate_up = torch.empty(E, 2 * I, H, dtype=runtime.dtype, device=runtime.device)
             self.w_down = torch.empty(E, H, I, dtype=runtime.dtype, device=runtime.device)
             for e in range(E):
-                self.w_gate_up[e, :I].copy_(read(f"{self.base}.{e}.{self.n['gate']}.weight"))
-                self.w_gate_up[e, I:].copy_(read(f"{self.base}.{e}.{self.n['up']}.weight"))
-                self.w_down[e].copy_(read(f"{self.base}.{e}.{self.n['down']}.weight"))
+                self.w_gate_up[e, :I].copy_(read(self._expert(e, "gate")))
+                self.w_gate_up[e, I:].copy_(read(self._expert(e, "up")))
+                self.w_down[e].copy_(read(self._expert(e, "down")))
 
     def expected_experts_read(self, rows: int) -> float:
         """Distinct experts that `rows` rows choose when every expert is as likely as any other."""
@@ -206,7 +228,7 @@ class SigmoidTopKExperts(Part):
         """What the norm kernel in front of the layer needs to run this layer's router on its `rows` output rows
         (for many rows the kernel norms several rows per block, so the router's weights are read once per block)."""
         return {"weight": self.w_router, "bias": self.expert_bias, "k": self.top_k, "normalize": self.normalize,
-                "scoring": self.scoring, "floor": self.norm_floor, "scale": self.scale,
+                "scoring": self.scoring, "groups": self.groups, "floor": self.norm_floor, "scale": self.scale,
                 "ids": torch.empty(rows, self.top_k, dtype=torch.int32, device=device),
                 "wts": torch.empty(rows, self.top_k, dtype=torch.float32, device=device)}
 
@@ -218,7 +240,7 @@ class SigmoidTopKExperts(Part):
         ids = torch.empty(R, self.top_k, dtype=torch.int32, device=x32.device)
         wts = torch.empty(R, self.top_k, dtype=torch.float32, device=x32.device)
         ops.router_topk(logits, self.expert_bias, self.top_k, self.normalize, self.norm_floor, self.scale, ids, wts,
-                        self.scoring)
+                        self.scoring, self.groups)
         return ids, wts
 
     def plan_for(self, pairs: int, device, tile_rows: int | None = None) -> ops.MoePlan:
@@ -241,6 +263,8 @@ class SigmoidTopKExperts(Part):
         if step is not None and step.trace is not None:
             step.trace.setdefault("routes", []).append((self.prefix, ids))
         tc = self.runtime.tensorcore
+        if self.gate_constants is not None:
+            ops.gate_constants(*self.gate_constants)
         if tc is not None and x.dtype == torch.bfloat16:
             rows = tc.experts(self, x, ids, wts)
             if rows is not None:
@@ -253,3 +277,66 @@ class SigmoidTopKExperts(Part):
         y = torch.empty(R * self.top_k, H, dtype=torch.float32, device=x.device)
         ops.gemm_simt_grouped(act, None, 1, self.w_down, y, plan, swiglu=False)
         return ops.ExpertRows(y, plan.pos_of_pair, ids, wts)
+
+
+@register_part("feed_forward", "shared_and_routed")
+class SharedAndRouted(Part):
+    """A routed feed-forward beside a dense one that every row uses: out = routed(n) + sigmoid(gate n) * shared(n), the gate
+    one number a row (`shared_gate`: the name of its [1, hidden] matrix; None: no gate). `routed` and `shared` are specs of
+    feed-forward kinds of their own. The sum is not formed here: the three pieces go on as `ops.GatedSum`, which a norm
+    behind the branch adds in its own kernel (`ops.materialize` forms it for anything else)."""
+
+    def __init__(self, spec, prefix: str = "", hidden_size: int = 0, **_):
+        super().__init__(spec, prefix, hidden_size)
+        self.routed = FEED_FORWARDS[spec["routed"].kind](spec["routed"], prefix=prefix, hidden_size=hidden_size)
+        self.shared = FEED_FORWARDS[spec["shared"].kind](spec["shared"], prefix=prefix, hidden_size=hidden_size)
+        self.gate_name = prefix + spec["shared_gate"] if spec.get("shared_gate") else None
+        self.w_gate = None
+
+    @property
+    def graph_safe(self) -> bool:
+        return self.routed.graph_safe and self.shared.graph_safe
+
+    def weight_specs(self, present=None):
+        out = self.routed.weight_specs(present) + self.shared.weight_specs(present)
+        if self.gate_name:
+            out.append(TensorSpec(self.gate_name, (1, self.hidden_size)))
+        return out
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        self.routed.bind(read, runtime)
+        self.shared.bind(read, runtime)
+        if self.gate_name:
+            self.w_gate = runtime.matrix(read(self.gate_name))
+
+    # the routed part's accounts and records are this part's
+    def expected_experts_read(self, rows: int) -> float:
+        return self.routed.expected_experts_read(rows)
+
+    def step_bytes(self, elem: int, experts_read: float | None = None, rows: int = 1, **_) -> int:
+        return (self.routed.step_bytes(elem, experts_read=experts_read, rows=rows) + self.shared.step_bytes(elem)
+                + (self.hidden_size * elem if self.gate_name else 0))
+
+    def count_into(self, counts) -> None:
+        self.routed.count_into(counts)
+
+    @property
+    def num_experts(self) -> int:
+        return self.routed.num_experts
+
+    def router_args(self, rows: int, device):
+        return self.routed.router_args(rows, device)
+
+    def forward_from(self, norm, residual, delta, step):
+        route = self.routed.router_args(residual.shape[0], residual.device)
+        x = norm.add_norm(residual, delta, route=route)
+        return self.forward(x, step, routing=(route["ids"], route["wts"]))
+
+    def forward(self, x, step, routing=None):
+        routed = self.routed.forward(x, step, routing=routing)
+        shared = self.shared.forward(x, step)
+        gate = None
+        if self.w_gate is not None:
+            gate = ops.gemm_simt(x, self.w_gate, None, torch.empty(x.shape[0], 1, dtype=torch.float32, device=x.device))
+        return ops.GatedSum(shared, gate, routed)

@@ -38,6 +38,11 @@ class DecoderModel:
             out.append(TensorSpec(s.head_name, (s.vocab_size, s.hidden_size)))
         for layer in self.layers:
             out += layer.weight_specs(present)
+        seen = set()
+        for site in s.schedule:             # vectors the run order adds to the stream between layers
+            if site.add is not None and site.add.tensor not in seen:
+                seen.add(site.add.tensor)
+                out.append(TensorSpec(site.add.tensor, (site.add.rows, s.hidden_size), role="vector", init="bias"))
         return out
 
     def load(self, weights, runtime: Runtime) -> "DecoderModel":
@@ -53,6 +58,10 @@ class DecoderModel:
         self.final_norm.bind(weights.read, runtime)
         for layer in self.layers:
             layer.bind(weights.read, runtime)
+        self.stream_adds = {}
+        for site in s.schedule:
+            if site.add is not None and site.add.tensor not in self.stream_adds:
+                self.stream_adds[site.add.tensor] = runtime.vector(weights.read(site.add.tensor))
         return self
 
     def weight_bytes(self) -> int:
@@ -124,6 +133,9 @@ class DecoderModel:
                     layer = self.layers[site.layer]
                     torch.cuda.nvtx.range_push(f"site {i} layer {site.layer} {type(layer.mixer).__name__} + "
                                                f"{type(layer.feed_forward).__name__}")
+                if site.add is not None:
+                    # (what is pending is added by the layer's first norm; the order of the two additions is free)
+                    ops.add_vector(residual, self.stream_adds[site.add.tensor][site.add.row])
                 pending = self.layers[site.layer].run(residual, pending, step, cache, writes_cache=own)
                 if ranges:
                     torch.cuda.nvtx.range_pop()

@@ -23,7 +23,7 @@ class RMSNorm(Part):
         super().__init__(spec, prefix)
         self.size = size
         self.eps = float(spec["eps"])
-        self.name = prefix + "weight"
+        self.name = prefix + str(spec.get("tensor") or "weight")     # `tensor`: the weight's own name behind the prefix
         self.weight = None
 
     def weight_specs(self, present=None):
@@ -50,6 +50,21 @@ class RMSNorm(Part):
         out32 = torch.empty(rows, self.size, dtype=torch.float32, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, gather, out32, route)
         return out, out32
+
+
+    def add_normed(self, residual: torch.Tensor, delta, gate: torch.Tensor | None = None, experts=None, then=None,
+                   gather: torch.Tensor | None = None, n_out: int | None = None):
+        """This norm behind a branch: residual += weight * d / rms(d), d the branch output `delta` (a tensor or a deferred
+        form; times sigmoid(gate[r]) with `gate`; plus the weighed rows of `experts`). `then`: the RMS norm in front of
+        the next sublayer, whose rows of the new residual are returned (the same kernel makes them; with `gather` only
+        of those rows, and the residual stays as it was)."""
+        if then is None:
+            ops.add_normed(residual, delta, self.weight, self.eps, gate, experts)
+            return None
+        rows = residual.shape[0] if gather is None else (n_out if n_out is not None else gather.shape[0])
+        out = torch.empty(rows, self.size, dtype=self.runtime.dtype, device=residual.device)
+        g = gather[:rows] if gather is not None else None
+        return ops.add_normed(residual, delta, self.weight, self.eps, gate, experts, (then.weight, then.eps, out, g))
 
 
 @register_part("norm", "dyt")

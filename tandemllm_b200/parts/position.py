@@ -5,6 +5,11 @@ rotated part share a frequency: x' = x cos + rotate_half(x) sin with rotate_half
 (engine/models/lfm2_moe/ref.py:84, 111-120). The frequencies are computed here once, in 32-bit, by the
 reference's expression; the angles, sines and cosines are computed in the kernel in 32-bit per row.
 
+`rope_pairs`: the interleaved layout: entries 2i and 2i + 1 of the rotated part are a pair, (u, v) at position p becomes
+(u cos a - v sin a, v cos a + u sin a) with a = p * theta^(-2i/d), for the first d = `rotary_dim` entries (the rest pass).
+The frequencies are formed once in 64-bit and rounded to 32-bit; angles, sines and cosines are 32-bit in the kernel. A
+mixer whose kernel turns pairs asks `fused_rotary_pairs()`.
+
 `none`: q and k are left as they are.
 
 An encoding either hands the fused q/k kernel its table (`fused_rotary`), or is applied by the mixer
@@ -41,6 +46,35 @@ class RotaryNeox(Part):
 
     def apply(self, q, k, positions):
         raise NotImplementedError("rope_neox is applied by the fused q/k kernel")
+
+
+@register_part("position_encoding", "rope_pairs")
+class RotaryPairs(Part):
+    graph_safe = True
+
+    def __init__(self, spec, head_dim: int = 0, **_):
+        super().__init__(spec)
+        self.theta = float(spec["theta"])
+        d = spec.get("rotary_dim")
+        self.rotary_dim = int(head_dim if d is None else d)
+        if self.rotary_dim % 2 or not 0 <= self.rotary_dim <= head_dim:
+            raise ValueError(f"rotary size {self.rotary_dim} for a rotated part of {head_dim}: an even size up to it")
+        self.inv_freq = None
+
+    def bind(self, read, runtime):
+        self.runtime = runtime
+        d = self.rotary_dim
+        inv = self.theta ** (-torch.arange(0, d, 2, dtype=torch.float64) / max(d, 1))
+        self.inv_freq = inv.to(torch.float32).to(runtime.device)
+
+    def fused_rotary(self):
+        return None
+
+    def fused_rotary_pairs(self):
+        return self.inv_freq, self.rotary_dim
+
+    def apply(self, q, k, positions):
+        raise NotImplementedError("rope_pairs is applied by the mixer's own kernel")
 
 
 @register_part("position_encoding", "none")
