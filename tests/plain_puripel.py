@@ -70,12 +70,11 @@ def mamba2_mixer(h, m, w, p, eps):
     decay = torch.exp(-torch.exp(w[p + "A_log"]) * dt)              # [T, H]
     y = torch.zeros(T, H, P, dtype=h.dtype)
     S = torch.zeros(H, N, P, dtype=h.dtype)
-    per = H // G
+    group = torch.arange(H) // (H // G)                              # head -> its group's B and C
     for t in range(T):
-        for hd in range(H):
-            g = hd // per
-            S[hd] = decay[t, hd] * S[hd] + dt[t, hd] * torch.outer(B[t, g], x[t, hd])
-            y[t, hd] = S[hd].T @ C[t, g] + w[p + "D"][hd] * x[t, hd]
+        Bt, Ct = B[t, group], C[t, group]                            # [H, N]
+        S = decay[t, :, None, None] * S + dt[t, :, None, None] * Bt[:, :, None] * x[t, :, None, :]
+        y[t] = torch.einsum("hnp,hn->hp", S, Ct) + w[p + "D"][:, None] * x[t]
     y = y.reshape(T, inner) * silu(z)
     parts = m["norm_groups"]
     y = rms_norm(y.view(T, parts, inner // parts), None, eps).reshape(T, inner) * w[p + "norm"]
@@ -133,10 +132,46 @@ def route(h, w, p, r):
     return ids, wts
 
 
-def moe(h, mlp, w, p):
+def choice_margin(h, w, p, r):
+    """How far the router's decisions are from going the other way: the smallest gap between the last chosen and the
+    first unchosen choice score of a row and, with groups, between the last kept and the first dropped group's score."""
+    E, top = r["experts"], r["top"]
+    s = torch.sigmoid(h @ w[p + "router"].T)
+    choice = s + w[p + "correction"] if (p + "correction") in w else s.clone()
+    gap = math.inf
+    groups = r.get("groups")
+    if groups and groups["keep"] < groups["count"]:
+        per = E // groups["count"]
+        gs = choice.view(-1, groups["count"], per).topk(min(2, per), dim=-1).values.sum(-1).sort(dim=-1, descending=True).values
+        gap = float((gs[:, groups["keep"] - 1] - gs[:, groups["keep"]]).min())
+        kept = gs[:, groups["keep"] - 1:groups["keep"]]
+        full = choice.view(-1, groups["count"], per).topk(min(2, per), dim=-1).values.sum(-1)
+        allowed = (full >= kept)[:, :, None].expand(-1, -1, per).reshape(-1, E)
+        choice = choice.masked_fill(~allowed, -math.inf)
+    if top < E:
+        c = choice.sort(dim=-1, descending=True).values
+        d = c[:, top - 1] - c[:, top]
+        gap = min(gap, float(d[torch.isfinite(d)].min()) if torch.isfinite(d).any() else math.inf)
+    return gap
+
+
+def greedy(cfg, weights, prompt, n):
+    """The n tokens the model continues `prompt` with when it always takes the most likely one."""
+    text = list(prompt)
+    for _ in range(n):
+        text.append(int(forward(cfg, weights, text)[-1].argmax()))
+    return text[len(prompt):]
+
+
+def moe(h, mlp, w, p, forced=None):
+    """`forced` (ids [T, top]): the experts to use instead of the router's own choice; the weights follow the ids."""
     T = h.shape[0]
     r = mlp["router"]
     ids, wts = route(h, w, p, r)
+    if forced is not None:
+        ids = torch.as_tensor(forced, dtype=torch.long)
+        s = torch.sigmoid(h @ w[p + "router"].T).gather(1, ids)
+        wts = s / (s.sum(-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
     out = torch.zeros_like(h)
     limit = mlp["expert"]["limit"]
     for t in range(T):
@@ -161,8 +196,13 @@ def run_order(cfg):
     return order + [(i, None) for i in range(b, n)]
 
 
-def forward(cfg, weights, tokens, layer_outputs: list | None = None):
-    """Logits float64 [T, vocab] of one sequence; `layer_outputs` collects the residual stream after every layer run."""
+def forward(cfg, weights, tokens, layer_outputs: list | None = None, routes: list | None = None, margins: list | None = None,
+            halves: bool = False):
+    """Logits float64 [T, vocab] of one sequence; `layer_outputs` collects the residual stream after every layer run.
+    `routes`: for every routed feed-forward in run order, the expert ids [T, top] to use instead of the router's choice.
+    `margins` collects, for every routed feed-forward run, the smallest gap between a chosen and an unchosen choice score.
+    With `halves`, `layer_outputs` also gets the stream after every mixer's half of a layer."""
+    routes = list(routes) if routes is not None else None
     w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -179,9 +219,13 @@ def forward(cfg, weights, tokens, layer_outputs: list | None = None):
         else:
             raise ValueError(layer["type"])
         x = x + rms_norm(d, w[p + "norm1b"], eps)
+        if layer_outputs is not None and halves:
+            layer_outputs.append(x.clone())
         if layer.get("mlp"):
             n = rms_norm(x, w[p + "norm2"], eps)
-            x = x + rms_norm(moe(n, layer["mlp"], w, p + "mlp."), w[p + "norm2b"], eps)
+            if margins is not None:
+                margins.append(choice_margin(n, w, p + "mlp.", layer["mlp"]["router"]))
+            x = x + rms_norm(moe(n, layer["mlp"], w, p + "mlp.", routes.pop(0) if routes else None), w[p + "norm2b"], eps)
         if layer_outputs is not None:
             layer_outputs.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["embed"].T

@@ -1,0 +1,548 @@
+"""Puripel on the GPU against the plain implementation (`tests/plain_puripel.py`): every mechanism alone at the kernels' own
+entry points, then whole models through the step function, the scheduler and the replay program.
+
+The tiny models (`tests/puripel_configs.py`) differ from one another in every size and constant, and the layers of one
+model differ among themselves. Where random weights would hide a fault (one far key among hundreds, a window's edge), one
+query and one key are scaled up so that one score stands out. A routed feed-forward's choice is a decision: where the
+engine's own rounding may take another expert than 64-bit arithmetic would (bfloat16), the engine records what it chose
+and the plain model is run with that choice forced, so every other number is still held to the tolerance; in 32-bit the
+choice itself is compared.
+
+Tolerances as for the engine's other models: 32-bit within 1e-4 of a row's largest magnitude, bfloat16 within 3e-2.
+"""
+
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import plain_puripel as P
+from tests import puripel_configs as C
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOL = {"float32": 1e-4, "bfloat16": 3e-2}
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+DEV = "cuda"
+
+
+def rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float(((a - b).abs() / b.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)).max())
+
+
+def rel_rows(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return ((a - b).abs() / b.abs().amax(dim=-1, keepdim=True).clamp_min(1e-30)).amax(dim=-1)
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+def engine_of(name, dtype, pages=64, parallel=4, cfg=None, W=None, **kw):
+    from tandemllm_b200.config import PuripelConfig
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.weights.loader import DictWeights
+    cfg = cfg or C.CONFIGS[name]
+    W = W or C.weights(name, bf16_exact=True)
+    spec = PuripelConfig.from_dict(cfg).to_spec()
+    args = EngineArgs(dtype=dtype, max_len=4096, parallel=parallel, block_size=16, kv_blocks=pages, graph=False, **kw)
+    return Engine._build(None, spec, DictWeights({k: v.clone() for k, v in W.items()}), args), cfg, W
+
+
+# ------------------------------------------------------------------------------------------ mechanisms alone
+@pytest.mark.parametrize("C_,K", [(40, 2), (33, 4), (300, 3), (7, 1)])
+def test_the_causal_convolution_over_portions_and_its_state(C_, K):
+    """Two requests side by side, one fed in portions of 1, 2 and 5 rows, the other whole: the outputs are the plain
+    convolution's, whatever the cut, and the slot holds the last K - 1 inputs."""
+    from tandemllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(C_ + K)
+    Ta, Tb = 8, 6
+    xa, xb = torch.randn(Ta, C_ + 3, generator=g), torch.randn(Tb, C_ + 3, generator=g)
+    taps, bias = torch.randn(C_, K, generator=g), torch.randn(C_, generator=g)
+    want_a = P.silu(P.causal_conv(xa[:, 3:].double(), taps.double(), bias.double()))
+    want_b = P.silu(P.causal_conv(xb[:, 3:].double(), taps.double(), bias.double()))
+    state = torch.zeros(3, (K - 1) * C_ + 11, device=DEV)           # slots of more than the convolution's floats
+    got_a, got_b = [], None
+    at = 0
+    for n in (1, 2, 5):
+        rows = torch.cat([xa[at:at + n], xb] if at == 0 else [xa[at:at + n]]).to(DEV)
+        both = at == 0
+        out = torch.empty(rows.shape[0], C_, device=DEV)
+        slot, start = i32([2, 0] if both else [2]), i32([0, n, n + Tb] if both else [0, n])
+        req = i32([0] * n + ([1] * Tb if both else []))
+        ops.causal_conv_act(rows[:, 3:], C_, taps.to(DEV), bias.to(DEV), state, slot, req, start, out, "silu")
+        ops.conv_state(rows[:, 3:], C_, K, state, slot, start, 2 if both else 1)
+        got_a.append(out[:n].cpu())
+        if both:
+            got_b = out[n:].cpu()
+        at += n
+    assert rel(torch.cat(got_a), want_a) < 1e-5 and rel(got_b, want_b) < 1e-5
+    if K > 1:
+        assert torch.equal(state[2, :(K - 1) * C_].cpu().view(K - 1, C_), xa[Ta - (K - 1):, 3:])
+        assert torch.equal(state[0, :(K - 1) * C_].cpu().view(K - 1, C_), xb[Tb - (K - 1):, 3:])
+    assert float(state[1].abs().max()) == 0 and float(state[:, (K - 1) * C_:].abs().max()) == 0
+
+
+@pytest.mark.parametrize("H,Pc,N,G", [(3, 12, 5, 1), (4, 8, 16, 4), (2, 40, 128, 1), (6, 20, 33, 3), (1, 64, 256, 1), (2, 16, 1, 2)])
+def test_the_state_space_recurrence_token_by_token_and_in_portions(H, Pc, N, G):
+    from tandemllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(H * 100 + N)
+    T = 37
+    inner = H * Pc
+    xbc = torch.randn(T, inner + 2 * G * N, generator=g)
+    dt = torch.randn(T, H + 2, generator=g)
+    dt_bias, a_log, d = 0.5 * torch.randn(H, generator=g), 0.7 * torch.randn(H, generator=g) - 0.5, 1 + torch.randn(H, generator=g)
+    # the plain recurrence
+    x, B, Cm = xbc[:, :inner].double().view(T, H, Pc), xbc[:, inner:inner + G * N].double().view(T, G, N), \
+        xbc[:, inner + G * N:].double().view(T, G, N)
+    step = P.softplus(dt[:, 1:1 + H].double() + dt_bias.double())
+    decay = torch.exp(-torch.exp(a_log.double()) * step)
+    S = torch.zeros(H, N, Pc, dtype=torch.float64)
+    want = torch.zeros(T, H, Pc, dtype=torch.float64)
+    group = torch.arange(H) // (H // G)
+    for t in range(T):
+        S = decay[t, :, None, None] * S + step[t, :, None, None] * B[t, group][:, :, None] * x[t, :, None, :]
+        want[t] = torch.einsum("hnp,hn->hp", S, Cm[t, group]) + d.double()[:, None] * x[t]
+    offset = 9
+    for cuts in ([T], [1] * T, [2, 17, 1, 16, 1]):
+        state = torch.zeros(2, offset + H * Pc * N, device=DEV)
+        got, at = [], 0
+        for n in cuts:
+            y = torch.empty(n, inner, device=DEV)
+            ops.ssm_scan(xbc[at:at + n].to(DEV).contiguous(), dt[at:at + n].to(DEV)[:, 1:1 + H], dt_bias.to(DEV), a_log.to(DEV),
+                         d.to(DEV), state, offset, i32([1]), i32([0, n]), 1, y, H, Pc, N, G)
+            got.append(y.cpu())
+            at += n
+        assert rel(torch.cat(got), want.view(T, inner)) < 2e-5, cuts
+        assert rel(state[1, offset:].cpu().view(H, Pc, N), S.transpose(1, 2)) < 2e-5
+        assert float(state[0].abs().max()) == 0 and float(state[1, :offset].abs().max()) == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_gate_comes_before_the_norm_of_each_part(dtype):
+    from tandemllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(2)
+    for inner, parts in [(48, 4), (36, 1), (120, 3)]:
+        y, zfull = torch.randn(5, inner, generator=g), torch.randn(5, inner + 7, generator=g)
+        w = 1 + 0.3 * torch.randn(inner, generator=g)
+        out = torch.empty(5, inner, dtype=DT[dtype], device=DEV)
+        ops.gated_group_norm(y.to(DEV), zfull.to(DEV)[:, :inner], w.to(DEV), 1e-3, parts, out)
+        v = y.double() * P.silu(zfull[:, :inner].double())
+        want = P.rms_norm(v.view(5, parts, -1), None, 1e-3).reshape(5, inner) * w.double()
+        assert rel(out.float(), want) < (1e-5 if dtype == "float32" else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [44, 128])
+def test_the_norm_behind_a_branch_with_every_form_of_branch_output(dtype, hidden):
+    from tandemllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(hidden)
+    R, k = 6, 3
+    res = torch.randn(R, hidden, generator=g)
+    parts = torch.randn(2, R, hidden, generator=g)
+    w, w2 = 1 + 0.3 * torch.randn(hidden, generator=g), 1 + 0.3 * torch.randn(hidden, generator=g)
+    gate = torch.randn(R, 1, generator=g)
+    rows = torch.randn(R * k, hidden, generator=g)
+    ids = torch.stack([torch.randperm(8, generator=g)[:k] for _ in range(R)]).to(torch.int32)
+    wts = torch.rand(R, k, generator=g)
+    pos = torch.randperm(R * k, generator=g).to(torch.int32)
+    routed = torch.stack([sum(wts[r, j].double() * rows[pos[r * k + j]].double() for j in range(k)) for r in range(R)])
+    dense = parts.double().sum(0)
+    er = ops.ExpertRows(rows.to(DEV), pos.to(DEV), ids.to(DEV), wts.to(DEV))
+    ps = ops.PartialSums(parts.to(DEV).contiguous().view(-1), 2, R, hidden)
+    for delta, gt, ex, want in [(parts[0].to(DEV), None, None, parts[0].double()), (ps, None, None, dense),
+                                (ps, gate.to(DEV), er, dense * torch.sigmoid(gate.double()) + routed), (None, None, er, routed)]:
+        r1 = res.clone().to(DEV)
+        ops.add_normed(r1, delta, w.to(DEV), 1e-5, gt, ex)
+        new = res.double() + P.rms_norm(want, w.double(), 1e-5)
+        assert rel(r1, new) < 1e-5
+        # with the next norm in the same kernel, and for chosen rows only
+        r2 = res.clone().to(DEV)
+        out = torch.empty(R, hidden, dtype=DT[dtype], device=DEV)
+        ops.add_normed(r2, delta, w.to(DEV), 1e-5, gt, ex, (w2.to(DEV), 1e-4, out, None))
+        assert rel(r2, new) < 1e-5
+        assert rel(out.float(), P.rms_norm(new, w2.double(), 1e-4)) < (1e-5 if dtype == "float32" else 1e-2)
+        r3 = res.clone().to(DEV)
+        some = torch.empty(2, hidden, dtype=DT[dtype], device=DEV)
+        ops.add_normed(r3, delta, w.to(DEV), 1e-5, gt, ex, (w2.to(DEV), 1e-4, some, i32([4, 1])))
+        assert torch.equal(r3.cpu(), res)
+        assert rel(some.float(), P.rms_norm(new[[4, 1]], w2.double(), 1e-4)) < (1e-5 if dtype == "float32" else 1e-2)
+    r4 = res.clone().to(DEV)
+    vec = torch.randn(3, hidden, generator=g).to(DEV)
+    ops.add_vector(r4, vec[1])
+    assert torch.equal(r4.cpu(), res + vec[1].cpu())
+
+
+@pytest.mark.parametrize("E,top,groups", [(6, 1, (3, 1)), (16, 4, (8, 3)), (8, 3, (2, 1)), (64, 6, (8, 4)), (160, 8, (16, 5)),
+                                          (10, 2, (5, 4)), (4, 4, (2, 2)), (12, 2, None), (9, 2, (9, 3))])
+def test_the_choice_within_the_best_groups(E, top, groups):
+    """The router's kernel alone and the one inside the norm's kernel against the plain choice: groups scored by their two
+    best (one when a group is one expert), corrections that are negative, weights from the uncorrected scores."""
+    from tandemllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(E + top)
+    R, hidden = 50, 32
+    x = torch.randn(R, hidden, generator=g)
+    wr = torch.randn(E, hidden, generator=g) * 0.4
+    corr = torch.randn(E, generator=g) * 0.5 - 1.0
+    r = {"experts": E, "top": top, "scale": 1.7}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    w = {"x.router": wr.double(), "x.correction": corr.double()}
+    ids_want, wts_want = P.route(x.double(), w, "x.", r)
+    assert P.choice_margin(x.double(), w, "x.", r) > 1e-5
+    logits = (x.double() @ wr.double().T).float().to(DEV)
+    ids = torch.empty(R, top, dtype=torch.int32, device=DEV)
+    wts = torch.empty(R, top, device=DEV)
+    ops.router_topk(logits, corr.to(DEV), top, True, 1e-20, 1.7, ids, wts, "sigmoid", groups)
+    assert torch.equal(ids.cpu().long(), ids_want)
+    assert rel(wts, wts_want) < 1e-5
+    # inside the norm: few rows (one row a block) and many
+    for rows in (3, R):
+        res = x[:rows].clone().to(DEV)
+        route = {"weight": wr.to(DEV), "bias": corr.to(DEV), "k": top, "normalize": True, "scoring": "sigmoid", "groups": groups,
+                 "floor": 1e-20, "scale": 1.7, "ids": torch.empty(rows, top, dtype=torch.int32, device=DEV),
+                 "wts": torch.empty(rows, top, device=DEV)}
+        out = torch.empty(rows, hidden, device=DEV)
+        ops.add_rmsnorm(res, None, torch.ones(hidden, device=DEV), 1e-6, out, None, None, route)
+        n = P.rms_norm(x[:rows].double(), None, 1e-6)
+        if P.choice_margin(n, w, "x.", r) > 1e-5:
+            iw, ww = P.route(n, w, "x.", r)
+            assert torch.equal(route["ids"].cpu().long(), iw)
+            assert rel(route["wts"], ww) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_clamped_gate_of_an_expert(dtype):
+    """g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(1.702 g') (u' + 1): in the unfused kernel, in the 32-bit
+    grouped product and, in bfloat16, in the gated epilogues of the tensor-core products, for few rows and many."""
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.parts.base import Runtime
+    from tandemllm_b200.parts.feed_forward import SwiGLU
+    from tandemllm_b200.config import PartSpec
+    g = torch.Generator().manual_seed(4)
+    gu = (3 * torch.randn(9, 2 * 20, generator=g)).to(DT[dtype])
+    out = torch.empty(9, 20, dtype=DT[dtype], device=DEV)
+    ops.gate_constants(1.3, 1.702)
+    ops.gated_mul(gu.to(DEV), out, ops.ACTIVATIONS["clamped_swish"])
+    gg, uu = gu.double()[:, :20].clamp(max=1.3), gu.double()[:, 20:].clamp(-1.3, 1.3)
+    assert rel(out.float(), gg * torch.sigmoid(1.702 * gg) * (uu + 1)) < (1e-5 if dtype == "float32" else 1e-2)
+    rt = Runtime(torch.device(DEV), DT[dtype])
+    if dtype == "bfloat16":
+        from tandemllm_b200.kernels import tensorcore
+        tensorcore.enable(rt)
+    for hidden, inter, limit in [(64, 48, 0.9), (128, 256, 2.0)]:
+        part = SwiGLU(PartSpec("swiglu", {"intermediate_size": inter, "activation": "clamped_swish", "gate_limit": limit,
+                                          "gate_slope": 1.702, "weight_suffix": "", "names": {"gate": "g", "up": "u", "down": "d"}}),
+                      prefix="s.", hidden_size=hidden)
+        W = {"s.g": torch.randn(inter, hidden, generator=g) * 0.3, "s.u": torch.randn(inter, hidden, generator=g) * 0.3,
+             "s.d": torch.randn(hidden, inter, generator=g) * 0.1}
+        W = {k: v.to(torch.bfloat16).float() for k, v in W.items()}
+        part.bind(lambda n: W[n], rt)
+        for rows in (1, 7, 200):
+            x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).float()
+            got = ops.materialize(part.forward(x.to(DEV).to(DT[dtype]), None))
+            want = P.expert(x.double(), {"s.gate": W["s.g"].double(), "s.up": W["s.u"].double(), "s.down": W["s.d"].double()},
+                            "s.", limit)
+            assert rel(got.float(), want) < (1e-5 if dtype == "float32" else 2e-2), (hidden, rows)
+
+
+def _latent_setup(H, D, Rr, V, L, Q, width, g, dtype):
+    from tandemllm_b200.parts.base import Runtime
+    rt = Runtime(torch.device(DEV), DT[dtype])
+    if dtype == "bfloat16":
+        from tandemllm_b200.kernels import tensorcore
+        tensorcore.enable(rt)
+    names = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "out": "o"}
+    shapes = {"dq": (Q, width), "dq.norm": (Q,), "uq": (H * (D + Rr), Q), "dkv": (L + Rr, width), "dkv.norm": (L,),
+              "uk": (H * D, L), "uv": (H * V, L), "o": (width, H * V)}
+    W = {}
+    for k, s in shapes.items():
+        t = torch.randn(s, generator=g)
+        t = 1 + 0.2 * t if k.endswith("norm") else t * s[-1] ** -0.5
+        W["m." + k] = t.to(torch.bfloat16).float()
+    return rt, names, W
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,D,Rr,V,L,Q,window,dims", [(3, 8, 6, 10, 20, 12, 5, 4), (4, 32, 16, 24, 64, 48, 40, 16), (9, 16, 8, 16, 33, 24, 0, 8),
+                                                      (2, 64, 32, 64, 128, 64, 64, 32), (1, 4, 2, 3, 300, 16, 17, 2)])
+def test_latent_attention_sees_its_window_and_nothing_else(dtype, H, D, Rr, V, L, Q, window, dims):
+    """The mixer alone against the plain one, fed whole, in portions and token by token on shuffled pages; then one key
+    made to stand out just inside and just outside the window, and far back."""
+    from tandemllm_b200.config import PartSpec
+    from tandemllm_b200.parts.base import PagedSiteCache, StepContext
+    from tandemllm_b200.parts.latent_attention import LatentAttentionMixer
+    g = torch.Generator().manual_seed(H * 7 + L)
+    width, T, page = 40, 150, 16
+    rt, names, W = _latent_setup(H, D, Rr, V, L, Q, width, g, dtype)
+    m = {"heads": H, "dim": D, "rot_dim": Rr, "vdim": V, "kv_rank": L, "q_rank": Q, "scale": 0.19, "rot": {"base": 50.0, "dims": dims}}
+    if window:
+        m["mask"] = {"size": window}
+    spec = PartSpec("latent_attention", {"num_heads": H, "head_dim": D, "rot_dim": Rr, "value_dim": V, "kv_rank": L, "q_rank": Q,
+                                         "scale": 0.19, "window": window or None, "eps": 1e-5, "names": names,
+                                         "position": PartSpec("rope_pairs", {"theta": 50.0, "rotary_dim": dims})})
+    mixer = LatentAttentionMixer(spec, prefix="m.", hidden_size=width)
+    mixer.bind(lambda n: W[n], rt)
+    x = torch.randn(T, width, generator=g).to(torch.bfloat16).float()
+    w64 = {k: v.double() for k, v in W.items()}
+
+    def run(xs, cuts):
+        pages = torch.randperm(12, generator=g)[:-(-T // page)].to(torch.int32)
+        cache_t = torch.zeros(12, 1, page, L + Rr, dtype=DT[dtype], device=DEV)
+        cache = PagedSiteCache(0, page, cache_t, cache_t)
+        table = torch.full((2, 16), -1, dtype=torch.int32)
+        table[1, :pages.numel()] = pages
+        out, at = [], 0
+        for n in cuts:
+            step = StepContext(n_rows=n, n_requests=1, token_ids=None, positions=i32(list(range(at, at + n))), req_of_row=i32([1] * n),
+                               row_start=i32([0, n]), state_slot=i32([0]), block_tables=[table.to(DEV)], out_rows=None, n_out=0,
+                               max_rows_per_request=n, max_context=at + n)
+            from tandemllm_b200.kernels import ops
+            out.append(ops.materialize(mixer.forward(xs[at:at + n].to(DEV).to(DT[dtype]), step, cache)).float().cpu())
+            at += n
+        assert int(rt.status.item()) == 0
+        return torch.cat(out)
+
+    want = P.latent_attention_mixer(x.double(), m, w64, "m.", 1e-5)
+    tol = 1e-4 if dtype == "float32" else 5e-2       # (a chain of five rounded products, held against rows of a few numbers)
+    for cuts in ([T], [2, 61, 1, 1, 30, 3, 52], [100] + [1] * 50):
+        assert rel(run(x, cuts), want) < tol, cuts
+    # one key that every head's query of the last row looks for: inside the window it decides the output, outside not
+    last = T - 1
+    for back in ([window - 1, window, last] if window else [1, 77, last]):
+        if back > last:
+            continue
+        x2 = x.clone()
+        x2[last - back] *= 6.0
+        want2 = P.latent_attention_mixer(x2.double(), m, w64, "m.", 1e-5)
+        got2 = run(x2, [T - 1, 1])
+        assert rel(got2[-1:], want2[-1:]) < tol, back
+        seen = not window or back < window
+        changed = rel(want2[-1:], want[-1:]) > 1e-6
+        assert changed == seen, back
+
+
+# ------------------------------------------------------------------------------------------ whole models
+def run_schedule(engine, requests, schedule, routes=None):
+    """`schedule`: steps of [(request, count), ...]; every position's logits are wanted. Returns request -> logits. With
+    `routes` (a dict) the steps are traced and routes[request] becomes, for every routed feed-forward in run order, the
+    expert ids [positions, top] the engine chose."""
+    from tandemllm_b200.engine import StepEntry
+    at = {r: 0 for r in requests}
+    got = {r: [] for r in requests}
+    if routes is not None:
+        engine.step_function.trace = {}
+    for step in schedule:
+        entries = []
+        for r, n in step:
+            if not engine.cache.has(r):
+                engine.admit(r)
+            entries.append(StepEntry(r, requests[r][at[r]:at[r] + n], list(range(n))))
+        logits = engine.step(entries).float().cpu()
+        chosen = [ids.cpu() for _, ids in engine.step_function.trace.get("routes", [])] if routes is not None else []
+        o = 0
+        for r, n in step:
+            got[r].append(logits[o:o + n])
+            if routes is not None:
+                per_site = routes.setdefault(r, [[] for _ in chosen])
+                for site, ids in enumerate(chosen):
+                    per_site[site].append(ids[o:o + n])
+            o += n
+            at[r] += n
+            if at[r] == len(requests[r]):
+                engine.release(r)
+    engine.step_function.trace = None
+    engine.cache.check()
+    if routes is not None:
+        for r in list(routes):
+            routes[r] = [torch.cat(v).long() for v in routes[r]]
+    return {r: torch.cat(v) for r, v in got.items()}
+
+
+def held_to_the_plain_model(engine, cfg, W, requests, schedule, dtype, what=""):
+    """Runs the schedule and compares every position of every request. 32-bit: against the plain model as it is (the
+    prompts are ones whose every choice of experts is clear of a tie). bfloat16: against the plain model following the
+    experts the engine chose."""
+    routes = {} if dtype == "bfloat16" else None
+    got = run_schedule(engine, requests, schedule, routes)
+    rows = []
+    for r, toks in requests.items():
+        want = P.forward(cfg, W, toks, routes=routes[r] if routes is not None else None)
+        if dtype == "float32":
+            assert rel(got[r], want) < TOL[dtype], (what, r)
+        rows.append(rel_rows(got[r], want))
+    if dtype == "bfloat16":
+        # These models norm parts of a row of a dozen numbers; where such a part happens to be small, its norm multiplies
+        # the rounding of what went in, on that row and the rows its state reaches. So in bfloat16 nine rows in ten (of
+        # all requests together) are held to the tolerance and every row to ten times that: a fault moves every row by
+        # its own size.
+        rows = torch.cat(rows)
+        assert float(rows.quantile(0.9)) < TOL[dtype] and float(rows.max()) < 10 * TOL[dtype], what
+    return got
+
+
+def cuts(n, sizes):
+    out, i = [], 0
+    while n:
+        c = min(n, sizes[i % len(sizes)])
+        out.append(c)
+        n -= c
+        i += 1
+    return out
+
+
+def clear_tokens(name, n, seed, cfg=None, W=None):
+    """A prompt of the tiny model whose every routing decision is clear of a tie by more than 32-bit rounding moves it
+    (the first of a few candidate prompts that is)."""
+    cfg, W = cfg or C.CONFIGS[name], W or C.weights(name)
+    for k in range(20):
+        toks = C.tokens(name, n, seed=seed + 1000 * k)
+        margins = []
+        P.forward(cfg, W, toks, margins=margins)
+        if min(margins, default=math.inf) > 2e-4:
+            return toks
+    raise AssertionError("no prompt clear of routing ties among 20 candidates")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["p1", "p2", "p3", "p4"])
+def test_whole_prompts_decoding_and_portions_agree_with_the_plain_model(name, dtype):
+    engine, cfg, W = engine_of(name, dtype)
+    toks = clear_tokens(name, 150, seed=3)
+    reqs = {"a": toks}
+    whole = held_to_the_plain_model(engine, cfg, W, reqs, [[("a", len(toks))]], dtype, "whole")["a"]
+    # the first tokens of a sequence alone
+    held_to_the_plain_model(engine, cfg, W, {"a": toks[:3]}, [[("a", 1)], [("a", 1)], [("a", 1)]], dtype, "first tokens")
+    # most of it at once, then token by token across windows' and pages' edges
+    held_to_the_plain_model(engine, cfg, W, reqs, [[("a", 60)]] + [[("a", 1)]] * 90, dtype, "decode")
+    # token by token from the very first
+    held_to_the_plain_model(engine, cfg, W, {"a": toks[:70]}, [[("a", 1)]] * 70, dtype, "every token alone")
+    # portions of changing size, down to two tokens
+    for sizes in ([2], [7, 2, 33, 3, 16, 5], [64, 2, 31]):
+        got = held_to_the_plain_model(engine, cfg, W, reqs, [[("a", c)] for c in cuts(len(toks), sizes)], dtype, f"portions {sizes}")["a"]
+        if dtype == "float32":          # how the prompt was cut changes nothing beyond rounding
+            assert rel(got, whole) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["p1", "p2", "p4"])
+def test_unequal_requests_in_one_batch_on_pages_and_slots_that_are_used_again(name, dtype):
+    """Seven requests of unequal length through four slots and a pool too small for all of them: portions beside single
+    tokens, requests that pause, pages and state slots that come back and are taken again (a slot's state must start at
+    zero for its next owner)."""
+    lengths = [90, 5, 47, 130, 1, 33, 64]
+    reqs = {f"q{i}": clear_tokens(name, n, seed=10 + i) for i, n in enumerate(lengths)}
+    engine, cfg, W = engine_of(name, dtype, pages=24, parallel=4)
+    rng = np.random.default_rng(0)
+    at = {r: 0 for r in reqs}
+    waiting, live, schedule = list(reqs), [], []
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        step = []
+        for r in list(live):
+            left = len(reqs[r]) - at[r]
+            if len(live) > 1 and rng.random() < 0.2:
+                continue                                    # left out of this step
+            n = min(left, int(rng.choice([1, 1, 2, 3, 16, 29])))
+            step.append((r, n))
+            at[r] += n
+            if at[r] == len(reqs[r]):
+                live.remove(r)
+        if step:
+            schedule.append(step)
+    held_to_the_plain_model(engine, cfg, W, reqs, schedule, dtype, "mixed")
+    stats = engine.cache.stats()
+    assert all(g["reused"] > 0 for g in stats["groups"] if g["window"] is None or g["window"] < 64)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_every_window(dtype):
+    name = "p1"
+    engine, cfg, W = engine_of(name, dtype, pages=12)
+    toks = clear_tokens(name, 400, seed=8)
+    held_to_the_plain_model(engine, cfg, W, {"a": toks}, [[("a", 9)]] + [[("a", 1)]] * 391, dtype, "long decoding")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_token_reaches_the_end_through_the_recurrent_state_only(dtype):
+    """A model whose attention windows are short: what the first token was still shows 200 tokens later, through the
+    state-space layers' states, in whole prompts, portions and decoding alike."""
+    name = "p1"
+    W = C.weights(name)
+    for key in W:                   # slow decays and small steps: a state that keeps what it saw for hundreds of tokens
+        if key.endswith(".A_log"):
+            W[key] = torch.full_like(W[key], -5.0)
+        elif key.endswith(".dt_bias"):
+            W[key] = torch.full_like(W[key], -1.0)
+    engine, cfg, W = engine_of(name, dtype, pages=16, W=W)
+    toks = clear_tokens(name, 200, seed=5, W=W)
+    other = [(toks[0] + 1) % cfg["vocab"]] + toks[1:]
+    a = P.forward(cfg, W, toks)[-1]
+    b = P.forward(cfg, W, other)[-1]
+    assert rel(a[None], b[None]) > 1e-3, "the tiny model forgets too fast for this test to show anything"
+    for sched in ([[("a", 200)]], [[("a", c)] for c in cuts(200, [31, 2])], [[("a", 150)]] + [[("a", 1)]] * 50):
+        held_to_the_plain_model(engine, cfg, W, {"a": toks}, sched, dtype, "far")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(dtype, tmp_path):
+    """A folder on disk (config.json chooses the architecture), `Engine.generate`, several requests at once, decode steps
+    from CUDA graphs where the engine takes them."""
+    from tandemllm_b200.engine import Engine, EngineArgs
+    from tandemllm_b200.sampling import SamplingParams
+    name = "p2"
+    folder = C.write_folder(str(tmp_path / "m"), name)
+    engine = Engine.from_folder(folder, EngineArgs(dtype=dtype, max_len=256, parallel=3, chunk_size=32, max_batched_tokens=64))
+    assert engine.model.spec.architecture == "Puripel"
+    prompts = [C.tokens(name, n, seed=40 + n) for n in (70, 3, 21, 45)]
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
+    cfg, W = C.CONFIGS[name], C.weights(name, bf16_exact=True)
+    for prompt, out in zip(prompts, outs):
+        assert len(out) == 12
+        # rounding may take another token where two logits are close, or another expert on the way: every token must be
+        # among the plain model's best given the text so far
+        text = list(prompt)
+        for t in out:
+            row = P.forward(cfg, W, text)[-1]
+            assert float(row.max() - row[t]) <= (2e-3 if dtype == "float32" else 0.12) * float(row.abs().max())
+            text.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_program_on_a_folder(dtype, tmp_path):
+    name = "p3"
+    folder = C.write_folder(str(tmp_path / "m"), name)
+    toks = {"x": clear_tokens(name, 40, seed=1), "y": clear_tokens(name, 19, seed=2)}
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks["x"][:25], "want": [0, 24]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": toks["x"][25:], "want": [14]},
+                                     {"id": "y", "tokens": toks["y"], "want": [18]}], "end": ["x", "y"]},
+             {"step": 2, "entries": [{"id": "z", "tokens": toks["y"][:2], "want": []}], "end": ["z"]}]
+    out = tmp_path / "out"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", dtype, "--out",
+                        str(out), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    V = C.CONFIGS[name]["vocab"]
+    a = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V))
+    b = torch.from_numpy(np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, V))
+    cfg, W = C.CONFIGS[name], C.weights(name)
+    routes = None
+    if dtype == "bfloat16":         # the same steps in this process tell which experts the engine chooses
+        routes = {}
+        run_schedule(engine_of(name, dtype, pages=8)[0], toks, [[("x", 25)], [("x", 15), ("y", 19)]], routes)
+    wx = P.forward(cfg, W, toks["x"], routes=routes["x"] if routes else None)
+    wy = P.forward(cfg, W, toks["y"], routes=routes["y"] if routes else None)
+    tol = TOL[dtype] if dtype == "float32" else 3 * TOL[dtype]
+    assert rel(a, wx[[0, 24]]) < tol
+    assert rel(b, torch.stack([wx[39], wy[18]])) < tol
+    assert not (out / "2.f32").exists()
