@@ -18,6 +18,7 @@ requests at a context of 8192 tokens. A "step" is one decode step of the whole b
   points     decoded tokens a second at batch 1 and 64 with their roofline fractions, and the headline batch without
              CUDA graphs
 
+`--design puripel` does the same for Puripel beside an LFM2 MoE model of short-convolution and attention layers.
 `--design sifupel` measures the Sifupel design beside the closest existing model (an LFM2 configuration of attention layers
 and dense feed-forwards only) at a few equal layer sizes: prefill and decode throughput, and every launch summed by kernel
 family with its fraction of the measured peak (its own line; the default workload and line are untouched).
@@ -363,7 +364,13 @@ class LaunchTimer:
                 "tl_add_dyt": "residual add + norm (Dynamic Tanh)", "tl_activation": "activation",
                 "tl_attention_headmix": "attention", "tl_attention_headmix_mma": "attention",
                 "tl_gated_mul": "gate activation", "tl_argmax": "argmax", "tl_sample": "sampling",
-                "tl_router_topk": "router top-k", "tl_moe_combine": "expert combine", "tl_kv_store": "cache write"}.get(name, name)
+                "tl_router_topk": "router top-k", "tl_moe_combine": "expert combine", "tl_kv_store": "cache write",
+                "tl_ssm_scan": "state-space recurrence", "tl_causal_conv_act": "causal conv + activation",
+                "tl_conv_state": "causal conv + activation", "tl_gated_group_norm": "gate + norm in parts",
+                "tl_latent_prepare": "latent norm + rotary + cache write", "tl_rmsnorm_rows": "latent norm + rotary + cache write",
+                "tl_head_linear": "products a head", "tl_attention_latent": "latent attention",
+                "tl_add_normed": "norm behind a branch + residual add (+ next norm)", "tl_add_vector": "vector onto the stream",
+                "tl_ssm_decode": "conv + state-space recurrence + gate + norm (decode)"}.get(name, name)
 
     def __enter__(self):
         torch = self.torch
@@ -593,6 +600,154 @@ def design_compare(a) -> int:
     return 0
 
 
+PURIPEL_SIZES = {
+    "1k": dict(width=1024, layers=8, vocab=32768, ssm_heads=32, cols=64, state=128, groups=4, taps=4, heads=16, dim=64, rot=32,
+               vdim=64, kv_rank=256, q_rank=512, window=1024, experts=32, top=4, ff=512, egroups=(4, 2), shared=1024),
+    "2k": dict(width=2048, layers=12, vocab=65536, ssm_heads=64, cols=64, state=128, groups=8, taps=4, heads=32, dim=128, rot=64,
+               vdim=128, kv_rank=512, q_rank=1024, window=2048, experts=64, top=6, ff=768, egroups=(8, 4), shared=1536),
+}
+
+
+def puripel_compare(a) -> int:
+    """Puripel beside the closest existing model, LFM2 MoE, at equal width, depth, vocabulary and experts: where Puripel has
+    a state-space layer the neighbour has its short convolution, where Puripel has latent attention the neighbour attends
+    with as many heads of dim + rot_dim over all keys. Random weights. For each: a prompt of `--prefill-tokens` tokens, decode
+    steps of `--batch` requests at a context of the window's length (device-timed, from CUDA graphs), and one eager decode
+    step and one prefill with every launch timed and summed by kernel family, with the work of Puripel's own kernels:
+    the recurrence 4 flops a (row, head, column, state row) on the CUDA cores; latent attention 2 (kv_rank + rot_dim) +
+    2 kv_rank flops a visible (row, key, head) and, decoding, the bytes of the visible cached rows; the heads' products."""
+    import torch
+
+    from tandemllm_b200.config import Lfm2MoeConfig, PuripelConfig
+    from tandemllm_b200.engine import Engine, EngineArgs, StepEntry
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.sampling import SamplingParams
+    pk = peaks()
+    tokens, batch = a.prefill_tokens, a.batch
+    elem = 2 if a.dtype == "bfloat16" else 4
+    out = []
+    for label in (a.design_sizes.split(",") if a.design_sizes else PURIPEL_SIZES):
+        z = PURIPEL_SIZES[label]
+        W, L, V = z["width"], z["layers"], z["vocab"]
+        mlp = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5,
+                                         "groups": {"count": z["egroups"][0], "keep": z["egroups"][1]}},
+               "expert": {"ff": z["ff"], "limit": 7.0}, "shared": {"ff": z["shared"], "limit": 7.0}}
+        ssm = {"type": "mamba2", "mlp": mlp, "mixer": {"heads": z["ssm_heads"], "vdim": z["cols"], "state": z["state"],
+                                                       "groups": z["groups"], "conv": z["taps"], "norm_groups": z["groups"]}}
+        att = {"type": "latent_attention", "mlp": mlp,
+               "mixer": {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["kv_rank"],
+                         "q_rank": z["q_rank"], "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": z["rot"]},
+                         "mask": {"size": z["window"]}}}
+        pur = PuripelConfig.from_dict({"architecture": "Puripel", "vocab": V, "width": W, "norm": {"eps": 1e-5},
+                                       "layers": [ssm if i % 2 == 0 else att for i in range(L)]})
+        hd = z["dim"] + z["rot"]
+        nd = 64 if hd <= 96 else 128                 # the neighbour's head size (its kernels take 64 and 128)
+        lfm = Lfm2MoeConfig.from_dict(dict(
+            CONFIG_8B, vocab_size=V, hidden_size=W, intermediate_size=z["shared"], moe_intermediate_size=z["ff"],
+            num_hidden_layers=L, num_attention_heads=z["heads"] * hd // nd, num_key_value_heads=max(1, z["heads"] * hd // nd // 4),
+            head_dim=nd, num_dense_layers=0, num_experts=z["experts"], num_experts_per_tok=z["top"],
+            layer_types=["conv" if i % 2 == 0 else "full_attention" for i in range(L)]))
+        context = z["window"]
+        row = {"sizes": dict(z, label=label), "prefill_tokens": tokens, "batch": batch, "context": context}
+        for name, cfg in (("puripel", pur), ("lfm2_moe", lfm)):
+            room = max(context, tokens) + 4 * a.steps + 64
+            engine = Engine.from_config(cfg, seed=0, args=EngineArgs(
+                dtype=a.dtype, max_len=room, parallel=batch, block_size=16, max_batched_tokens=max(tokens, batch),
+                chunk_size=tokens, graph=a.graph == "on"))
+            for sc in engine.cache.site_cache:
+                if hasattr(sc, "k"):
+                    sc.k.normal_(0, 0.5)
+                    if sc.v is not sc.k:
+                        sc.v.normal_(0, 0.5)
+            g = torch.Generator().manual_seed(1)
+            fn = engine.step_function
+
+            def prefill_once():
+                engine.admit("prefill")
+                prompt = torch.randint(0, V, (tokens,), generator=g).tolist()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                engine.step([StepEntry("prefill", prompt, [tokens - 1])])
+                e1.record()
+                torch.cuda.synchronize()
+                engine.release("prefill")
+                return e0.elapsed_time(e1)
+            prefill_once()
+            pre_ms = statistics.median(prefill_once() for _ in range(3))
+            timer = LaunchTimer()
+            with timer:
+                prefill_once()
+                pre_table = timer.table()
+            greedy = SamplingParams(temperature=0.0, max_tokens=1 << 30, ignore_eos=True)
+            reqs = [start_with_context(engine, torch.randint(0, V, (context,), generator=g).tolist(),
+                                       SamplingParams(**vars(greedy))) for _ in range(batch)]
+            fn.check_status = False
+            toks = torch.randint(0, V, (3 * a.steps + a.warmup + 4, batch), generator=g).tolist()
+            picked = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+            def one(i):
+                ops.argmax(fn.run([StepEntry(r.request_id, [toks[i][j]], [0]) for j, r in enumerate(reqs)]), picked)
+            for i in range(a.warmup):
+                one(i)
+            torch.cuda.synchronize()
+            regions = []
+            for rep in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for i in range(a.warmup + rep * a.steps, a.warmup + (rep + 1) * a.steps):
+                    one(i)
+                e1.record()
+                torch.cuda.synchronize()
+                regions.append(e0.elapsed_time(e1) / a.steps)
+            dec_ms = statistics.median(regions)
+            kept, fn.use_graphs = fn.use_graphs, False
+            one(3 * a.steps + a.warmup)
+            with timer:
+                one(3 * a.steps + a.warmup + 1)
+                dec_table = timer.table()
+            fn.use_graphs = kept
+            fn.check_status = True
+            fn.raise_on_fault()
+            for t in (pre_table, dec_table):
+                for r in t.values():
+                    r["ms"] = round(r["ms"], 4)
+            entry = {"prefill": {"ms": round(pre_ms, 3), "tok_s": round(tokens / pre_ms * 1e3, 1), "families": pre_table},
+                     "decode": {"ms_per_step": round(dec_ms, 4), "tok_s": round(batch / dec_ms * 1e3, 1),
+                                "weight_bytes_per_step": engine.model.decode_bytes(batch)["total"], "families": dec_table}}
+            entry["decode"]["frac_hbm_weights_only"] = round(entry["decode"]["weight_bytes_per_step"] / dec_ms / 1e6 / pk["hbm_gbs"], 4)
+            if name == "puripel":
+                n_ssm, n_att = (L + 1) // 2, L // 2
+                Hs, Pc, N, H, Lr, Dk = z["ssm_heads"], z["cols"], z["state"], z["heads"], z["kv_rank"], z["kv_rank"] + z["rot"]
+                pairs = sum(min(i + 1, z["window"]) for i in range(tokens))
+                work = {"state-space recurrence": {"prefill_flops": 4.0 * tokens * Hs * Pc * N * n_ssm,
+                                                   "decode_bytes": 8.0 * batch * Hs * Pc * N * n_ssm},
+                        "latent attention": {"prefill_flops": pairs * H * (2.0 * Dk + 2.0 * Lr) * n_att,
+                                             "decode_bytes": float(elem) * batch * min(context, z["window"]) * Dk * n_att},
+                        "products a head": {"prefill_flops": 2.0 * tokens * H * Lr * (z["dim"] + z["vdim"]) * n_att,
+                                            "decode_bytes": float(elem) * H * Lr * (z["dim"] + z["vdim"]) * n_att}}
+                for fam, wk in work.items():
+                    if fam in pre_table:
+                        ms = pre_table[fam]["ms"]
+                        pre_table[fam]["TFLOPs"] = round(wk["prefill_flops"] / ms / 1e9, 2)
+                    if fam in dec_table:
+                        ms = dec_table[fam]["ms"]
+                        dec_table[fam]["GBps"] = round(wk["decode_bytes"] / ms / 1e6, 1)
+                        dec_table[fam]["frac_hbm"] = round(wk["decode_bytes"] / ms / 1e6 / pk["hbm_gbs"], 4)
+            row[name] = entry
+            for r in reqs:
+                r.num_computed = engine.cache.length_of(r.request_id)
+                engine.scheduler.abort(r)
+            del engine, fn, reqs
+            torch.cuda.empty_cache()
+        out.append(row)
+    print(json.dumps({"design_compare": "puripel beside lfm2 moe (short convolution and attention layers, routed experts)",
+                      "dtype": a.dtype, "peaks": pk,
+                      "data": "synthetic: random weights, uniform random token ids, random cached rows as context",
+                      "rows": out}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -627,15 +782,16 @@ def main() -> int:
                     help="programmatic dependent launch between the kernels (for comparison; ordinary launches by default)")
     ap.add_argument("--profile", action="store_true",
                     help="bracket the timed decode steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    ap.add_argument("--design", choices=("sifupel",),
+    ap.add_argument("--design", choices=("sifupel", "puripel"),
                     help="measure this design beside the closest existing model at equal layer sizes (its own line)")
-    ap.add_argument("--design-sizes", default="", help="--design: which of " + ", ".join(DESIGN_SIZES) + " (default: all)")
+    ap.add_argument("--design-sizes", default="", help="--design: which of " + ", ".join(DESIGN_SIZES) + " (sifupel) or "
+                    + ", ".join(PURIPEL_SIZES) + " (puripel) (default: all)")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm(a)
     if a.design:
         a.warmup = max(a.warmup, 3)
-        return design_compare(a)
+        return puripel_compare(a) if a.design == "puripel" else design_compare(a)
     if a.gpus != 1:
         print(json.dumps({"error": f"this engine runs on one GPU; --gpus {a.gpus} is not implemented", "n_gpus": a.gpus}))
         return 2

@@ -83,6 +83,12 @@ def lib():
         l.tl_tc_token_tile.argtypes = [c_int, c_int]
         l.tl_tc_token_tile.restype = c_int
         l.tl_tc_last_error.restype = ctypes.c_char_p
+        l.tl_attention_latent_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, ctypes.c_float,
+                                              c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                              c_void_p, c_void_p]
+        l.tl_attention_latent_mma.restype = c_int
+        l.tl_attention_latent_mma_scratch.argtypes = [c_int, c_int, c_int, c_int]
+        l.tl_attention_latent_mma_scratch.restype = c_longlong
         l.tl_tc_set_gate_constants.argtypes = [ctypes.c_float, ctypes.c_float]
         l.tl_tc_set_gate_constants.restype = c_int
         l.tl_paged_attention_mma.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
@@ -305,6 +311,35 @@ class TensorCore:
             cache.k.shape[0], tiles.data_ptr(), tiles.shape[0], step.positions.data_ptr(), float(scale), int(window or 0),
             ops.ptr(mix), ops.ptr(gate), int(ld_gate), out.data_ptr(), Hq, Hk, D, self.status.data_ptr(), ops.stream()),
             "attention_headmix_mma")
+        return True
+
+    def attention_latent(self, q, cache, table, step, scale, window, out, latent: int, runtime) -> bool:
+        """Latent attention on the tensor cores (csrc/attention_latent_mma.cu): q float32 [rows, heads, latent + rotated part],
+        out bfloat16 [rows, heads, latent]. Steps of few rows and long contexts are cut into spans of keys, a CTA each, so
+        that the GPU is filled; False when the cache is not bfloat16."""
+        R, H, Dk = q.shape
+        if cache.k.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or latent > 512 or Dk > 1024:
+            return False
+        tiles = -(-(R * H) // 64) + step.n_requests if step.max_rows_per_request > 1 else step.n_requests * -(-H // 64)
+        chunks = -(-latent // 256)
+        reach = min(step.max_context, window + 31) if window else step.max_context
+        n_spans, span = 1, 0
+        ctas = tiles * chunks
+        if step.max_rows_per_request * H <= 64 and reach > 128 and ctas < 2 * self.sm_count:
+            wanted = max(1, (2 * self.sm_count) // ctas)
+            span = max(64, -(-(-(-reach // wanted)) // 32) * 32)
+            n_spans = -(-step.max_context // span)
+            if n_spans == 1:
+                span = 0
+        scratch = None
+        if n_spans > 1:
+            scratch = runtime.scratch("attention", lib().tl_attention_latent_mma_scratch(R, H, latent, n_spans))
+        _check(lib().tl_attention_latent_mma(
+            q.data_ptr(), cache.k.data_ptr(), table.data_ptr(), table.shape[1], cache.page_size, cache.k.shape[0],
+            step.req_of_row.data_ptr(), step.row_start.data_ptr(), step.positions.data_ptr(), float(scale), int(window or 0),
+            out.data_ptr(),
+            ops.ptr(scratch), R, step.n_requests, tiles, H, latent, Dk, n_spans, span, self.status.data_ptr(), ops.stream()),
+            "attention_latent_mma", kernels=2 if n_spans > 1 else 1)
         return True
 
     def in_proj_conv(self, x, w_in, b_in, taps, b_taps, state, state_slot, req_of_row, positions, y,

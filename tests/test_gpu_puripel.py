@@ -273,7 +273,7 @@ def _latent_setup(H, D, Rr, V, L, Q, width, g, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H,D,Rr,V,L,Q,window,dims", [(3, 8, 6, 10, 20, 12, 5, 4), (4, 32, 16, 24, 64, 48, 40, 16), (9, 16, 8, 16, 33, 24, 0, 8),
-                                                      (2, 64, 32, 64, 128, 64, 64, 32), (1, 4, 2, 3, 300, 16, 17, 2)])
+                                                      (2, 64, 32, 64, 128, 64, 64, 32), (1, 4, 2, 3, 300, 16, 17, 2), (20, 8, 8, 8, 72, 32, 130, 8)])
 def test_latent_attention_sees_its_window_and_nothing_else(dtype, H, D, Rr, V, L, Q, window, dims):
     """The mixer alone against the plain one, fed whole, in portions and token by token on shuffled pages; then one key
     made to stand out just inside and just outside the window, and far back."""
@@ -312,7 +312,8 @@ def test_latent_attention_sees_its_window_and_nothing_else(dtype, H, D, Rr, V, L
         return torch.cat(out)
 
     want = P.latent_attention_mixer(x.double(), m, w64, "m.", 1e-5)
-    tol = 1e-4 if dtype == "float32" else 5e-2       # (a chain of five rounded products, held against rows of a few numbers)
+    # (bfloat16: a chain of five rounded products and the rounded weights of the softmax, held against rows of a few numbers)
+    tol = 1e-4 if dtype == "float32" else 8e-2
     for cuts in ([T], [2, 61, 1, 1, 30, 3, 52], [100] + [1] * 50):
         assert rel(run(x, cuts), want) < tol, cuts
     # one key that every head's query of the last row looks for: inside the window it decides the output, outside not
