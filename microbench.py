@@ -8,6 +8,8 @@
     python microbench.py norm --rows 8
     python microbench.py headmix --batch 8 --window 1024
     python microbench.py headmix --batch 1 --rows 2048 --window 1024
+    python microbench.py scan --rows 2048
+    python microbench.py latent --rows 2048 --context 2048 --window 1024
 
 Sizes default to the LFM2-8B-A1B layer (hidden 2048, 32 experts of width 1792 top-4, 32/8 heads of 64). Inputs are
 larger than the 126 MB L2 or a 256 MB buffer is written between timed launches, so DRAM figures mean something; a
@@ -190,6 +192,54 @@ def headmix(a) -> dict:
             "flops": flops, "TFLOPs": flops / ms / 1e9, "kv_bytes": nbytes, "GBps": nbytes / ms / 1e6}
 
 
+def scan(a) -> dict:
+    """The state-space recurrence of one layer over one request's portion (chunked from 256 rows on) or a decode step."""
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.parts import Runtime
+    ops.core()
+    rt = Runtime(torch.device(DEV), torch.float32)
+    H, Pc, N, G, B, R = a.heads, a.cols, a.state, a.groups, a.batch, a.rows
+    inner = H * Pc
+    xbc = torch.randn(B * R, inner + 2 * G * N, device=DEV)
+    dt = torch.randn(B * R, H, device=DEV)
+    vecs = [torch.randn(H, device=DEV) * 0.3 for _ in range(3)]
+    state = torch.zeros(B, H * Pc * N, device=DEV)
+    y = torch.empty(B * R, inner, device=DEV)
+    slot = torch.arange(B, dtype=torch.int32, device=DEV)
+    start = torch.arange(0, (B + 1) * R, R, dtype=torch.int32, device=DEV)
+    ms = timed(lambda: ops.ssm_scan(xbc, dt, vecs[0], vecs[1] - 1.0, vecs[2], state, 0, slot, start, B, y, H, Pc, N, G,
+                                    max_rows_per_request=R, runtime=rt), a.iters)
+    flops = 4.0 * B * R * H * Pc * N
+    nbytes = 4.0 * (xbc.numel() + dt.numel() + y.numel() + 2 * state.numel())
+    return {"kernel": "state-space recurrence", "batch": B, "rows": R, "heads": H, "cols": Pc, "state": N, "ms": ms,
+            "flops": flops, "TFLOPs_fp32": flops / ms / 1e9, "bytes": nbytes, "GBps": nbytes / ms / 1e6}
+
+
+def latent(a) -> dict:
+    """Latent attention of one layer on the tensor cores: `batch` requests of `rows` rows at a context of `context`."""
+    from tandemllm_b200.parts import PagedSiteCache, StepContext
+    rt = runtime()
+    H, L, Rr, B, R, ctx, win, page = a.heads, a.kv_rank, a.rot_dim, a.batch, a.rows, a.context, a.window, 16
+    Dk = L + Rr
+    pages_each = -(-ctx // page)
+    cache_t = (torch.randn(B * pages_each, 1, page, Dk, device=DEV) * 0.5).to(torch.bfloat16)
+    cache = PagedSiteCache(0, page, cache_t, cache_t)
+    table = torch.arange(B * pages_each, dtype=torch.int32, device=DEV).view(B, pages_each)
+    q = torch.randn(B * R, H, Dk, device=DEV)
+    out = torch.empty(B * R, H, L, dtype=torch.bfloat16, device=DEV)
+    pos = torch.cat([torch.arange(ctx - R, ctx, dtype=torch.int32) for _ in range(B)]).to(DEV)
+    req = torch.arange(B, dtype=torch.int32).repeat_interleave(R).to(DEV)
+    start = torch.arange(0, (B + 1) * R, R, dtype=torch.int32, device=DEV)
+    step = StepContext(n_rows=B * R, n_requests=B, token_ids=None, positions=pos, req_of_row=req, row_start=start, state_slot=None,
+                       block_tables=[table], out_rows=None, n_out=0, max_rows_per_request=R, max_context=ctx)
+    ms = timed(lambda: rt.tensorcore.attention_latent(q, cache, table, step, Dk ** -0.5, win, out, L, rt), a.iters)
+    pairs = B * sum(min(p + 1, win) if win else p + 1 for p in range(ctx - R, ctx))
+    flops = pairs * H * (2.0 * Dk + 2.0 * L)
+    nbytes = 2.0 * B * min(ctx, (win + R) if win else ctx) * Dk + q.numel() * 4 + out.numel() * 2
+    return {"kernel": "latent attention (mma.sync)", "batch": B, "rows": R, "context": ctx, "window": win, "heads": H, "kv_rank": L,
+            "rot_dim": Rr, "ms": ms, "flops": flops, "TFLOPs": flops / ms / 1e9, "bytes": nbytes, "GBps": nbytes / ms / 1e6}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="what", required=True)
@@ -225,16 +275,32 @@ def main(argv=None) -> int:
     hm.add_argument("--heads", type=int, default=32)
     hm.add_argument("--kv-heads", type=int, default=8)
     hm.add_argument("--head-dim", type=int, default=64)
+    sc = sub.add_parser("scan")
+    sc.add_argument("--batch", type=int, default=1)
+    sc.add_argument("--rows", type=int, default=2048)
+    sc.add_argument("--heads", type=int, default=32)
+    sc.add_argument("--cols", type=int, default=64)
+    sc.add_argument("--state", type=int, default=128)
+    sc.add_argument("--groups", type=int, default=4)
+    la = sub.add_parser("latent")
+    la.add_argument("--batch", type=int, default=1)
+    la.add_argument("--rows", type=int, default=2048)
+    la.add_argument("--context", type=int, default=2048)
+    la.add_argument("--window", type=int, default=1024)
+    la.add_argument("--heads", type=int, default=16)
+    la.add_argument("--kv-rank", type=int, default=256)
+    la.add_argument("--rot-dim", type=int, default=32)
     n = sub.add_parser("norm")
     n.add_argument("--rows", type=int, default=8)
     n.add_argument("--hidden", type=int, default=2048)
     for p in (e, d):
         p.add_argument("--product", default="pair", choices=("pair", "single"),
                        help="prompt-sized products: the kernel on pairs of SMs (cta_group::2), or the one-CTA persistent kernel")
-    for p in (e, d, t, n, hm):
+    for p in (e, d, t, n, hm, sc, la):
         p.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)
-    result = {"expert_gemm": expert_gemm, "dense_gemm": dense_gemm, "attention": attention, "norm": norm, "headmix": headmix}[a.what](a)
+    result = {"expert_gemm": expert_gemm, "dense_gemm": dense_gemm, "attention": attention, "norm": norm, "headmix": headmix,
+              "scan": scan, "latent": latent}[a.what](a)
     print(json.dumps({k: (round(v, 4) if isinstance(v, float) else v) for k, v in result.items()}))
     return 0
 

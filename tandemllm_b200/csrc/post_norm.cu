@@ -101,6 +101,19 @@ __global__ void __launch_bounds__(256) add_normed_kernel(PostNormParams p) {
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[c] = from_f32<T>(row[c] * inv2 * p.pre_weight[c]);
 }
 
+// out[r] = x[r, :] . w: a warp a row (a projection onto one number a row, such as the logit of a gate)
+template <typename T>
+__global__ void __launch_bounds__(256) row_dot_kernel(const T* __restrict__ x, long long ld_x, const T* __restrict__ w,
+                                                      float* __restrict__ out, int rows, int hidden) {
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const T* xr = x + (long long)r * ld_x;
+  float acc = 0.f;
+  for (int c = lane; c < hidden; c += 32) acc = fmaf(to_f32(xr[c]), to_f32(w[c]), acc);
+  acc = warp_sum(acc);
+  if (lane == 0) out[r] = acc;
+}
+
 // residual[r, :] += vec
 __global__ void add_vector_kernel(float* __restrict__ residual, const float* __restrict__ vec, long long n, int hidden) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
@@ -137,6 +150,16 @@ extern "C" int tl_add_normed(float* residual, const float* delta, int parts, lon
     if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     add_normed_kernel<bf16><<<rows, 256, smem, stream>>>(p);
   }
+  TL_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int tl_row_dot(const void* x, long long ld_x, const void* w, float* out, int rows, int hidden, int dtype,
+                          cudaStream_t stream) {
+  if (rows == 0) return 0;
+  TL_REQUIRE(rows > 0 && hidden > 0 && x && w && out, "row dot: %d rows of %d", rows, hidden);
+  if (dtype == TL_FP32) row_dot_kernel<float><<<ceil_div(rows, 8), 256, 0, stream>>>((const float*)x, ld_x, (const float*)w, out, rows, hidden);
+  else row_dot_kernel<bf16><<<ceil_div(rows, 8), 256, 0, stream>>>((const bf16*)x, ld_x, (const bf16*)w, out, rows, hidden);
   TL_LAUNCH_CHECK();
   return 0;
 }

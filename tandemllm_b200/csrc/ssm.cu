@@ -78,14 +78,24 @@ struct ScanParams {
   float* y;                  // [rows, H P]
   int H, P, N, G;
   int write_state;
+  // Long portions are cut into chunks of `chunk_tokens` rows that run side by side (0: a request's rows one after the other):
+  //   mode 1: every chunk runs from a zero state, writes no y, and leaves its last state and the product of its decays;
+  //   (tl_ssm_chunk_states then walks a request's chunks: each chunk's slot receives the state the chunk starts from,
+  //   S <- decay_c S + last_c, and the request's slot the state after the last chunk)
+  //   mode 2: every chunk runs from the state it starts from and writes its y.
+  int mode, chunk_tokens, max_chunks;
+  float* chunk_state;        // [requests * max_chunks, H, P, N]
+  float* chunk_decay;        // [requests * max_chunks, H]
 };
 
 constexpr int SCAN_LANES = 8;       // lanes that share a column of the state: lane l holds n = l, l + 8, ...
 constexpr int SCAN_COLS = 16;       // columns (values of p) a block
 constexpr int SCAN_TOKENS = 16;     // tokens staged at a time
 
-// grid (ceil(P / 16), H, requests), 128 threads: thread (col, lane) holds NPER entries of column p of S.
-template <int NPER>
+// grid (ceil(P / 16), H, requests), 128 threads: thread (col, lane) holds NPER entries of column p of S: with VEC (the
+// state's rows a multiple of 4) entries 4 lane .. 4 lane + 3 of every run of 32, read from shared memory 16 bytes at a
+// time, else entries lane, lane + 8, ...
+template <int NPER, bool VEC>
 __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanParams p) {
   extern __shared__ __align__(16) float sm[];
   const int N = p.N, P = p.P;
@@ -99,15 +109,28 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
   const int pcol = blockIdx.x * SCAN_COLS + col;
   const bool live = pcol < P;
   const int g = h / (p.H / p.G);
-  const int first = p.row_start[b], n_rows = p.row_start[b + 1] - first;
+  int first, n_rows;
+  float* st;
+  float* chunk_decay = nullptr;
+  if (p.mode == 0) {
+    first = p.row_start[b];
+    n_rows = p.row_start[b + 1] - first;
+    st = p.state + (long long)p.state_slot[b] * p.state_stride + ((long long)h * P + (live ? pcol : 0)) * N;
+  } else {
+    const int req = b / p.max_chunks, c = b - req * p.max_chunks;
+    first = p.row_start[req] + c * p.chunk_tokens;
+    n_rows = min(p.chunk_tokens, p.row_start[req + 1] - first);
+    st = p.chunk_state + ((long long)b * p.H * P + (long long)h * P + (live ? pcol : 0)) * N;
+    chunk_decay = p.chunk_decay + (long long)b * p.H + h;
+  }
   if (n_rows <= 0) return;
-  float* st = p.state + (long long)p.state_slot[b] * p.state_stride + ((long long)h * P + (live ? pcol : 0)) * N;
   float S[NPER];
 #pragma unroll
   for (int i = 0; i < NPER; ++i) {
-    const int n = lane + SCAN_LANES * i;
-    S[i] = (live && n < N) ? st[n] : 0.f;
+    const int n = VEC ? ((i >> 2) * 32 + lane * 4 + (i & 3)) : (lane + SCAN_LANES * i);
+    S[i] = (live && n < N && p.mode != 1) ? st[n] : 0.f;
   }
+  float decay_product = 1.f;
   const float neg_a = -expf(p.a_log[h]), bias = p.dt_bias[h], skip = p.d_skip[h];
   const long long xoff = (long long)h * P + (long long)blockIdx.x * SCAN_COLS;
   const long long boff = (long long)p.H * P + (long long)g * N;
@@ -115,11 +138,12 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
   for (int t0 = 0; t0 < n_rows; t0 += SCAN_TOKENS) {
     const int nt = min(SCAN_TOKENS, n_rows - t0);
     __syncthreads();
-    for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
-      const int t = i / N, n = i - t * N;
+    for (int t = 0; t < nt; ++t) {
       const float* src = p.xbc + (long long)(first + t0 + t) * p.ld_xbc;
-      sB[t * N + n] = src[boff + n];
-      sC[t * N + n] = src[coff + n];
+      for (int n = threadIdx.x; n < N; n += blockDim.x) {
+        sB[t * N + n] = src[boff + n];
+        if (p.mode != 1) sC[t * N + n] = src[coff + n];
+      }
     }
     for (int i = threadIdx.x; i < nt * SCAN_COLS; i += blockDim.x) {
       const int t = i / SCAN_COLS, c = i - t * SCAN_COLS;
@@ -131,18 +155,67 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
       sA[threadIdx.x] = expf(neg_a * d);
     }
     __syncthreads();
+    if (p.mode == 1) {              // the chunk's end state and its decays' product are all that is wanted
+      for (int t = 0; t < nt; ++t) {
+        const float a = sA[t];
+        const float dx = sDt[t] * sX[t * SCAN_COLS + col];
+        const float* Bt = sB + t * N;
+        decay_product *= a;
+        if constexpr (VEC) {
+#pragma unroll
+          for (int j = 0; j < NPER / 4; ++j) {
+            const int n = j * 32 + lane * 4;
+            if (n < N) {
+              const float4 b4 = *reinterpret_cast<const float4*>(Bt + n);
+              S[4 * j] = fmaf(a, S[4 * j], dx * b4.x);
+              S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * b4.y);
+              S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * b4.z);
+              S[4 * j + 3] = fmaf(a, S[4 * j + 3], dx * b4.w);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NPER; ++i) {
+            const int n = lane + SCAN_LANES * i;
+            if (n < N) S[i] = fmaf(a, S[i], dx * Bt[n]);
+          }
+        }
+      }
+      continue;
+    }
     for (int t = 0; t < nt; ++t) {
       const float a = sA[t], x = sX[t * SCAN_COLS + col];
       const float dx = sDt[t] * x;
       const float* Bt = sB + t * N;
       const float* Ct = sC + t * N;
       float acc = 0.f;
+      if constexpr (VEC) {
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < NPER; ++i) {
-        const int n = lane + SCAN_LANES * i;
-        if (n < N) {
-          S[i] = fmaf(a, S[i], dx * Bt[n]);
-          acc = fmaf(S[i], Ct[n], acc);
+        for (int j = 0; j < NPER / 4; ++j) {
+          const int n = j * 32 + lane * 4;
+          if (n < N) {
+            const float4 b4 = *reinterpret_cast<const float4*>(Bt + n);
+            const float4 c4 = *reinterpret_cast<const float4*>(Ct + n);
+            S[4 * j] = fmaf(a, S[4 * j], dx * b4.x);
+            S[4 * j + 1] = fmaf(a, S[4 * j + 1], dx * b4.y);
+            S[4 * j + 2] = fmaf(a, S[4 * j + 2], dx * b4.z);
+            S[4 * j + 3] = fmaf(a, S[4 * j + 3], dx * b4.w);
+            a0 = fmaf(S[4 * j], c4.x, a0);
+            a1 = fmaf(S[4 * j + 1], c4.y, a1);
+            a2 = fmaf(S[4 * j + 2], c4.z, a2);
+            a3 = fmaf(S[4 * j + 3], c4.w, a3);
+          }
+        }
+        acc = (a0 + a1) + (a2 + a3);
+      } else {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+          const int n = lane + SCAN_LANES * i;
+          if (n < N) {
+            S[i] = fmaf(a, S[i], dx * Bt[n]);
+            acc = fmaf(S[i], Ct[n], acc);
+          }
         }
       }
       acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -151,13 +224,37 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
       if (lane == 0 && live) p.y[(long long)(first + t0 + t) * ((long long)p.H * P) + (long long)h * P + pcol] = fmaf(skip, x, acc);
     }
   }
-  if (p.write_state && live) {
+  if (((p.mode == 0 && p.write_state) || p.mode == 1) && live) {
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
-      const int n = lane + SCAN_LANES * i;
+      const int n = VEC ? ((i >> 2) * 32 + lane * 4 + (i & 3)) : (lane + SCAN_LANES * i);
       if (n < N) st[n] = S[i];
     }
   }
+  if (p.mode == 1 && blockIdx.x == 0 && threadIdx.x == 0) *chunk_decay = decay_product;
+}
+
+// grid (ceil(H P N / 256), requests): a thread an entry of the state walks the request's chunks in order
+__global__ void __launch_bounds__(256) ssm_chunk_states_kernel(float* __restrict__ chunk_state, const float* __restrict__ chunk_decay,
+                                                               float* __restrict__ state, long long state_stride,
+                                                               const int* __restrict__ state_slot, const int* __restrict__ row_start,
+                                                               int H, int PN, int chunk_tokens, int max_chunks, int write_state) {
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  const long long per = (long long)H * PN;
+  if (e >= per) return;
+  const int h = (int)(e / PN);
+  const int chunks = ceil_div(row_start[b + 1] - row_start[b], chunk_tokens);
+  if (chunks <= 0) return;
+  float* slot = state + (long long)state_slot[b] * state_stride + e;
+  float S = *slot;
+  for (int c = 0; c < chunks; ++c) {
+    float* at = chunk_state + ((long long)b * max_chunks + c) * per + e;
+    const float last = *at;
+    *at = S;
+    S = fmaf(chunk_decay[((long long)b * max_chunks + c) * H + h], S, last);
+  }
+  if (write_state) *slot = S;
 }
 
 // grid (groups, rows): out[r, part] = w * v / rms(v), v = y * silu(z)
@@ -215,7 +312,7 @@ extern "C" int tl_conv_state(const float* in, long long ld_in, float* state, lon
 extern "C" int tl_ssm_scan(const float* xbc, long long ld_xbc, const float* dt, long long ld_dt, const float* dt_bias,
                            const float* a_log, const float* d_skip, float* state, long long state_stride,
                            const int* state_slot, const int* row_start, float* y, int requests, int H, int P, int N, int G,
-                           int write_state, cudaStream_t stream) {
+                           int write_state, int chunk_tokens, int max_chunks, float* chunk_scratch, cudaStream_t stream) {
   if (requests == 0) return 0;
   TL_REQUIRE(requests > 0 && requests <= 65535 && H > 0 && H <= 65535 && P > 0 && N > 0 && G > 0 && H % G == 0,
              "ssm scan: %d requests, %d heads in %d groups, columns %d, state %d", requests, H, G, P, N);
@@ -224,19 +321,53 @@ extern "C" int tl_ssm_scan(const float* xbc, long long ld_xbc, const float* dt, 
   p.xbc = xbc; p.ld_xbc = ld_xbc; p.dt = dt; p.ld_dt = ld_dt; p.dt_bias = dt_bias; p.a_log = a_log; p.d_skip = d_skip;
   p.state = state; p.state_stride = state_stride; p.state_slot = state_slot; p.row_start = row_start; p.y = y;
   p.H = H; p.P = P; p.N = N; p.G = G; p.write_state = write_state;
-  const dim3 grid(ceil_div(P, SCAN_COLS), H, requests), block(SCAN_COLS * SCAN_LANES);
+  p.mode = 0; p.chunk_tokens = chunk_tokens; p.max_chunks = max_chunks; p.chunk_state = nullptr; p.chunk_decay = nullptr;
+  const bool chunked = chunk_tokens > 0 && max_chunks > 1;
+  TL_REQUIRE(!chunked || (chunk_scratch && (long long)requests * max_chunks <= 65535), "ssm scan: %d requests in %d chunks each",
+             requests, max_chunks);
+  if (chunked) {
+    p.chunk_state = chunk_scratch;
+    p.chunk_decay = chunk_scratch + (long long)requests * max_chunks * H * P * N;
+  }
+  const dim3 grid(ceil_div(P, SCAN_COLS), H, chunked ? requests * max_chunks : requests), block(SCAN_COLS * SCAN_LANES);
   const size_t smem = (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_COLS + 2 * SCAN_TOKENS) * sizeof(float);
   const int per = ceil_div(N, SCAN_LANES);
-#define TL_SCAN(NPER_)                                              \
-  ssm_scan_kernel<NPER_><<<grid, block, smem, stream>>>(p)
-  if (per <= 2) TL_SCAN(2);
-  else if (per <= 4) TL_SCAN(4);
-  else if (per <= 8) TL_SCAN(8);
-  else if (per <= 16) TL_SCAN(16);
-  else TL_SCAN(32);
+  const bool vec = N % 4 == 0;
+#define TL_SCAN(NPER_)                                                                    \
+  do {                                                                                    \
+    if (vec) ssm_scan_kernel<(NPER_ < 4 ? 4 : NPER_), true><<<grid, block, smem, stream>>>(p); \
+    else ssm_scan_kernel<NPER_, false><<<grid, block, smem, stream>>>(p);                 \
+  } while (0)
+#define TL_SCAN_ANY()              \
+  do {                             \
+    if (per <= 2) TL_SCAN(2);      \
+    else if (per <= 4) TL_SCAN(4); \
+    else if (per <= 8) TL_SCAN(8); \
+    else if (per <= 16) TL_SCAN(16); \
+    else TL_SCAN(32);              \
+  } while (0)
+  if (!chunked) {
+    TL_SCAN_ANY();
+    TL_LAUNCH_CHECK();
+    return 0;
+  }
+  p.mode = 1;
+  TL_SCAN_ANY();
+  TL_LAUNCH_CHECK();
+  ssm_chunk_states_kernel<<<dim3((unsigned)ceil_div64((long long)H * P * N, 256), requests), 256, 0, stream>>>(
+      p.chunk_state, p.chunk_decay, state, state_stride, state_slot, row_start, H, P * N, chunk_tokens, max_chunks, write_state);
+  TL_LAUNCH_CHECK();
+  p.mode = 2;
+  TL_SCAN_ANY();
+#undef TL_SCAN_ANY
 #undef TL_SCAN
   TL_LAUNCH_CHECK();
   return 0;
+}
+
+// Floats of scratch a chunked scan needs.
+extern "C" long long tl_ssm_scan_scratch(int requests, int max_chunks, int H, int P, int N) {
+  return (long long)requests * max_chunks * ((long long)H * P * N + H);
 }
 
 extern "C" int tl_gated_group_norm(const float* y, const float* z, long long ld_z, const float* w, float eps, void* out,

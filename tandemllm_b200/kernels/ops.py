@@ -108,11 +108,12 @@ _SIGNATURES = {
     "tl_add_normed": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p,
                       c_int, c_void_p, c_float, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_add_vector": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "tl_row_dot": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_causal_conv_act": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_longlong, c_int, c_int, c_int, c_int, c_void_p],
     "tl_conv_state": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "tl_ssm_scan": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p,
-                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "tl_gated_group_norm": [c_void_p, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "tl_latent_prepare": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -148,6 +149,8 @@ def core():
             fn.restype = c_int
         lib.tl_headmix_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
         lib.tl_headmix_scratch_floats.restype = c_longlong
+        lib.tl_ssm_scan_scratch.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.tl_ssm_scan_scratch.restype = c_longlong
         lib.tl_last_error.restype = ctypes.c_char_p
         lib.tl_cuda_error_string.restype = ctypes.c_char_p
         lib.tl_cuda_error_string.argtypes = [c_int]
@@ -372,6 +375,16 @@ def add_normed(residual: torch.Tensor, delta, weight: torch.Tensor, eps: float, 
     return out
 
 
+def row_dot(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[r] . w in 32-bit: one number a row (w: a vector or a [1, hidden] matrix of x's type; out float32 [rows] or
+    [rows, 1])."""
+    _need(w, x.dtype, "w"); _need(out, torch.float32, "out")
+    if x.stride(-1) != 1 or w.numel() != x.shape[1] or out.numel() != x.shape[0]:
+        raise KernelError(f"row dot: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    check(core().tl_row_dot(ptr(x), x.stride(0), ptr(w), ptr(out), x.shape[0], x.shape[1], dtype_code(x.dtype), stream()), "row_dot")
+    return out
+
+
 def add_vector(residual: torch.Tensor, vec: torch.Tensor) -> None:
     """residual[r, :] += vec for every row."""
     _need(residual, torch.float32, "residual"); _need(vec, torch.float32, "vector")
@@ -404,18 +417,33 @@ def conv_state(x: torch.Tensor, channels: int, taps: int, state: torch.Tensor, s
                                channels, taps, stream()), "conv_state", kernels=1 if taps > 1 else 0)
 
 
+SCAN_CHUNK = 128            # rows of a chunk when a long portion's recurrence is cut into chunks that run side by side
+SCAN_CHUNKED_FROM = 256     # the longest portion of a step from which on it is
+
+
 def ssm_scan(xbc: torch.Tensor, dt: torch.Tensor, dt_bias, a_log, d_skip, state: torch.Tensor, state_offset: int, state_slot,
              row_start, requests: int, y: torch.Tensor, heads: int, cols: int, n_state: int, groups: int,
-             write_state: bool = True) -> torch.Tensor:
+             write_state: bool = True, max_rows_per_request: int = 0, runtime=None) -> torch.Tensor:
     """The selective state-space recurrence of csrc/ssm.cu over each request's rows. `xbc` float32 [rows, H P + 2 G N];
     `dt` a float32 view [rows, H] of the raw step sizes; a slot's recurrent state [H, P, N] begins `state_offset` floats
-    into its row of `state`; `y` float32 [rows, H P]."""
+    into its row of `state`; `y` float32 [rows, H P]. With `max_rows_per_request` (the step's longest portion) of
+    SCAN_CHUNKED_FROM rows or more and a `runtime` to keep the scratch, portions are cut into chunks of SCAN_CHUNK rows:
+    every chunk's own contribution from a zero state, the states the chunks start from, then every chunk's outputs."""
     _need(xbc, torch.float32, "xbc"); _need(y, torch.float32, "y"); _need(state, torch.float32, "state")
     if dt.dtype != torch.float32 or dt.stride(-1) != 1:
         raise KernelError("ssm scan: float32 step sizes with unit stride")
+    chunk = chunks = 0
+    scratch = None
+    if runtime is not None and max_rows_per_request >= SCAN_CHUNKED_FROM:
+        chunk, chunks = SCAN_CHUNK, -(-max_rows_per_request // SCAN_CHUNK)
+        if requests * chunks > 65535:
+            chunk = chunks = 0
+        else:
+            scratch = runtime.scratch("ssm_chunks", core().tl_ssm_scan_scratch(requests, chunks, heads, cols, n_state))
     check(core().tl_ssm_scan(ptr(xbc), xbc.stride(0), ptr(dt), dt.stride(0), ptr(dt_bias), ptr(a_log), ptr(d_skip),
                              state.data_ptr() + 4 * state_offset, state.stride(0), ptr(state_slot), ptr(row_start), ptr(y),
-                             requests, heads, cols, n_state, groups, int(write_state), stream()), "ssm_scan")
+                             requests, heads, cols, n_state, groups, int(write_state), chunk, chunks, ptr(scratch), stream()),
+          "ssm_scan", kernels=3 if chunks > 1 else 1)
     return y
 
 

@@ -338,5 +338,5 @@ class SharedAndRouted(Part):
         shared = self.shared.forward(x, step)
         gate = None
         if self.w_gate is not None:
-            gate = ops.gemm_simt(x, self.w_gate, None, torch.empty(x.shape[0], 1, dtype=torch.float32, device=x.device))
+            gate = ops.row_dot(x, self.w_gate, torch.empty(x.shape[0], 1, dtype=torch.float32, device=x.device))
         return ops.GatedSum(shared, gate, routed)

@@ -84,7 +84,7 @@ class SelectiveStateSpaceMixer(Part):
         y = torch.empty(R, inner, dtype=torch.float32, device=dev)
         ops.ssm_scan(xbc, proj[:, inner + self.channels:], self.dt_bias, self.a_log, self.d_skip, cache.state, self.conv_floats,
                      step.state_slot, step.row_start, step.n_requests, y, self.heads, self.cols, self.n_state, self.groups,
-                     write_state=writes_cache)
+                     write_state=writes_cache, max_rows_per_request=step.max_rows_per_request, runtime=self.runtime)
         v = torch.empty(R, inner, dtype=x.dtype, device=dev)
         ops.gated_group_norm(y, proj, self.w_norm, self.eps, self.norm_groups, v)
         return linear(self.runtime, v, self.w_out, out_dtype=torch.float32, defer=True)

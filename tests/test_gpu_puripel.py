@@ -126,6 +126,46 @@ def test_the_state_space_recurrence_token_by_token_and_in_portions(H, Pc, N, G):
         assert float(state[0].abs().max()) == 0 and float(state[1, :offset].abs().max()) == 0
 
 
+def test_long_portions_in_chunks_that_run_side_by_side():
+    """Three requests in one step, of 700, 1 and 300 rows, two of them with a state from before: the chunked form of the
+    recurrence (chunks of 128 rows from zero states, the states the chunks start from, then the outputs) against the plain
+    recurrence, and the slots afterwards."""
+    from tandemllm_b200.kernels import ops
+    from tandemllm_b200.parts.base import Runtime
+    rt = Runtime(torch.device(DEV), torch.float32)
+    g = torch.Generator().manual_seed(77)
+    H, Pc, N, G = 3, 20, 24, 1
+    inner = H * Pc
+    lengths, slots = [700, 1, 300], [2, 0, 3]
+    T = sum(lengths)
+    xbc = torch.randn(T, inner + 2 * G * N, generator=g)
+    dt = torch.randn(T, H, generator=g) - 1.0
+    dt_bias, a_log, d = 0.5 * torch.randn(H, generator=g), 0.7 * torch.randn(H, generator=g) - 2.0, 1 + torch.randn(H, generator=g)
+    offset = 5
+    state = torch.zeros(4, offset + H * Pc * N)
+    state[2, offset:] = torch.randn(H * Pc * N, generator=g)
+    state[0, offset:] = torch.randn(H * Pc * N, generator=g)
+    dev_state = state.clone().to(DEV)
+    y = torch.empty(T, inner, device=DEV)
+    starts = [0, 700, 701, 1001]
+    ops.ssm_scan(xbc.to(DEV), dt.to(DEV), dt_bias.to(DEV), a_log.to(DEV), d.to(DEV), dev_state, offset, i32(slots), i32(starts), 3,
+                 y, H, Pc, N, G, max_rows_per_request=700, runtime=rt)
+    for b, (n, slot) in enumerate(zip(lengths, slots)):
+        r0 = starts[b]
+        x, B, Cm = xbc[r0:r0 + n, :inner].double().view(n, H, Pc), xbc[r0:r0 + n, inner:inner + N].double(), \
+            xbc[r0:r0 + n, inner + N:].double()
+        step = P.softplus(dt[r0:r0 + n].double() + dt_bias.double())
+        decay = torch.exp(-torch.exp(a_log.double()) * step)
+        S = state[slot, offset:].double().view(H, Pc, N).transpose(1, 2).clone()
+        want = torch.zeros(n, H, Pc, dtype=torch.float64)
+        for t in range(n):
+            S = decay[t, :, None, None] * S + step[t, :, None, None] * B[t][None, :, None] * x[t, :, None, :]
+            want[t] = torch.einsum("hnp,n->hp", S, Cm[t]) + d.double()[:, None] * x[t]
+        assert rel(y[r0:r0 + n].cpu(), want.view(n, inner)) < 1e-4, b
+        assert rel(dev_state[slot, offset:].cpu().view(1, -1), S.transpose(1, 2).reshape(1, -1)) < 1e-4, b
+    assert torch.equal(dev_state[1].cpu(), state[1]) and torch.equal(dev_state[:, :offset].cpu(), state[:, :offset])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_gate_comes_before_the_norm_of_each_part(dtype):
     from tandemllm_b200.kernels import ops
