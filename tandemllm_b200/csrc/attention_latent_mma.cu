@@ -5,9 +5,10 @@
 // product, out = sum_j p_j c_j over the latent part of the keys.
 //
 // A CTA of four warps takes 64 consecutive (row, head) pairs of one request (a warp 16 of them) and walks the visible keys
-// in tiles of 32 aligned to absolute positions. A key tile is staged twice in shared memory: as it lies (the B operand of
-// Q K^T) and its latent part transposed (the B operand of P C). `mma.sync` m16n8k16, operands read from shared memory with
-// plain 32-bit loads from rows padded so that the eight rows a quad-pair reads fall into different banks. The latent's
+// in tiles of 32 aligned to absolute positions. A key tile is copied as it lies into one of two buffers in shared memory
+// (cp.async, 16 bytes a copy) while the tile before it is computed on; it is the B operand of Q K^T as it lies (plain
+// 32-bit loads) and, through ldmatrix with .trans, the B operand of P C. `mma.sync` m16n8k16; rows padded so that the
+// eight rows a load touches fall into different banks. The latent's
 // columns are taken in chunks of up to 256 (a CTA a chunk: the accumulators of one chunk are all a thread can hold), and,
 // for steps of few rows, the keys in spans aligned to absolute positions, each span a CTA of its own; a second kernel
 // joins the spans in order. One CTA finds its tile from the step's row_start by itself, so the launch needs no host list.
@@ -17,7 +18,6 @@ namespace tl {
 
 constexpr int LM_ROWS = 64;     // (row, head) pairs a CTA
 constexpr int LM_KEYS = 32;     // keys a tile
-constexpr int LM_VT = 40;       // a transposed latent column in shared memory: 32 keys and 8 of padding (20 words)
 
 struct LatentMmaParams {
   const float* q;            // [rows, H, Dk] 32-bit
@@ -53,9 +53,8 @@ template <int NT>
 __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                 // [64][qs]
-  bf16* sK = sQ + LM_ROWS * p.qs;                                // [32][qs]
-  bf16* sVt = sK + LM_KEYS * p.qs;                               // [8 NT][LM_VT]
-  __shared__ int s_pos[LM_ROWS], s_lo[LM_ROWS], s_page[LM_KEYS];
+  bf16* sK = sQ + LM_ROWS * p.qs;                                // two buffers of [32][qs], then some slack (see the launcher)
+  __shared__ int s_pos[LM_ROWS], s_lo[LM_ROWS], s_page[2][LM_KEYS];
   __shared__ int s_tile[4];                                      // request, its first row, its rows, first pair of the tile
   const int H = p.H, L = p.L, Dk = p.Dk, qs = p.qs;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -120,8 +119,14 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
   const int* tab = p.table + (long long)p.req_of_row[row_base] * p.max_pages;
   const bool vec = (Dk & 7) == 0 && ((uintptr_t)p.cache & 15) == 0;
   const int ksteps = p.Dkp >> 4;
-  for (int j0 = (key_lo / LM_KEYS) * LM_KEYS; j0 <= key_hi; j0 += LM_KEYS) {
-    __syncthreads();            // the tile before this one has been read
+  // Both key buffers' padding (the entries behind Dk that no copy touches) is zeroed once: the products read it.
+  for (int i = threadIdx.x; i < 2 * LM_KEYS * (qs - (Dk & ~7)); i += blockDim.x) {
+    const int per = qs - (Dk & ~7), rowi = i / per, c = (Dk & ~7) + (i - rowi * per);
+    if (c >= Dk) sK[(size_t)rowi * qs + c] = __float2bfloat16_rn(0.f);
+  }
+  // A tile's pages are looked up (lookup), then its rows are sent on their way into one of the two buffers (fetch: 16-byte
+  // cp.async copies where the rows allow them); the tile before it is computed on meanwhile.
+  auto lookup = [&](int j0, int which) {
     if (threadIdx.x < LM_KEYS) {
       const int j = j0 + threadIdx.x;
       int page = -1;
@@ -129,37 +134,52 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
         page = table_page(tab, j / p.page_size, p.max_pages, p.num_pages);
         if (page < 0) atomicExch(p.status, 3);
       }
-      s_page[threadIdx.x] = page;
+      s_page[which][threadIdx.x] = page;
     }
-    __syncthreads();
+  };
+  auto fetch = [&](int j0, int which) {
+    bf16* dst = sK + (size_t)which * LM_KEYS * qs;
     if (vec) {
-      const int per_row = qs >> 3;                               // 16-byte pieces of a staged row (the last one is padding)
+      const int per_row = Dk >> 3;                               // 16-byte pieces of a cached row
       for (int i = threadIdx.x; i < LM_KEYS * per_row; i += blockDim.x) {
         const int kk = i / per_row, c = (i - kk * per_row) << 3;
-        const int page = s_page[kk];
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (page >= 0 && c < Dk)
-          v = *reinterpret_cast<const uint4*>(p.cache + ((long long)page * p.page_size + (j0 + kk) % p.page_size) * Dk + c);
-        *reinterpret_cast<uint4*>(sK + (size_t)kk * qs + c) = v;
-        const bf16* e = reinterpret_cast<const bf16*>(&v);
-#pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          const int col = c + x - chunk0;
-          if (col >= 0 && col < NT * 8) sVt[col * LM_VT + kk] = (c + x < L) ? e[x] : __float2bfloat16_rn(0.f);
+        const int page = s_page[which][kk];
+        bf16* to = dst + (size_t)kk * qs + c;
+        if (page >= 0) {
+          const bf16* from = p.cache + ((long long)page * p.page_size + (j0 + kk) % p.page_size) * Dk + c;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(to)), "l"(from) : "memory");
+        } else {
+          *reinterpret_cast<uint4*>(to) = make_uint4(0u, 0u, 0u, 0u);
         }
       }
     } else {
-      for (int i = threadIdx.x; i < LM_KEYS * qs; i += blockDim.x) {
-        const int kk = i / qs, c = i - kk * qs;
-        const int page = s_page[kk];
-        bf16 v = __float2bfloat16_rn(0.f);
-        if (page >= 0 && c < Dk) v = p.cache[((long long)page * p.page_size + (j0 + kk) % p.page_size) * Dk + c];
-        sK[(size_t)kk * qs + c] = v;
-        const int col = c - chunk0;
-        if (col >= 0 && col < NT * 8) sVt[col * LM_VT + kk] = (c < L) ? v : __float2bfloat16_rn(0.f);
+      for (int i = threadIdx.x; i < LM_KEYS * Dk; i += blockDim.x) {
+        const int kk = i / Dk, c = i - kk * Dk;
+        const int page = s_page[which][kk];
+        dst[(size_t)kk * qs + c] = page >= 0 ? p.cache[((long long)page * p.page_size + (j0 + kk) % p.page_size) * Dk + c]
+                                             : __float2bfloat16_rn(0.f);
       }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int j_first = (key_lo / LM_KEYS) * LM_KEYS;
+  lookup(j_first, 0);
+  __syncthreads();
+  fetch(j_first, 0);
+  int which = 0;
+  for (int j0 = j_first; j0 <= key_hi; j0 += LM_KEYS, which ^= 1) {
+    const bool more = j0 + LM_KEYS <= key_hi;
+    if (more) lookup(j0 + LM_KEYS, which ^ 1);
     __syncthreads();
+    if (more) {
+      fetch(j0 + LM_KEYS, which ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();            // this tile's rows have landed, for every thread
+    const bf16* tK = sK + (size_t)which * LM_KEYS * qs;
+    const int* t_page = s_page[which];
     // S = Q K^T for the warp's 16 pairs and the tile's 32 keys
     float s[4][4];
 #pragma unroll
@@ -174,7 +194,7 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
       a[3] = q_hi[ks * 8 + 4 + t];
 #pragma unroll
       for (int n = 0; n < 4; ++n) {
-        const uint32_t* kr = reinterpret_cast<const uint32_t*>(sK + (size_t)(n * 8 + g) * qs);
+        const uint32_t* kr = reinterpret_cast<const uint32_t*>(tK + (size_t)(n * 8 + g) * qs);
         mma_bf16(s[n], a, kr[ks * 8 + t], kr[ks * 8 + 4 + t]);
       }
     }
@@ -185,7 +205,7 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int r = e >> 1, kk = n * 8 + 2 * t + (e & 1), j = j0 + kk;
-        const bool seen = s_page[kk] >= 0 && j >= my_lo[r] && j <= my_pos[r];
+        const bool seen = t_page[kk] >= 0 && j >= my_lo[r] && j <= my_pos[r];
         s[n][e] = seen ? s[n][e] * p.scale : -INFINITY;
         tile_max[r] = fmaxf(tile_max[r], s[n][e]);
       }
@@ -219,7 +239,8 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
       o[n][0] *= fix[0]; o[n][1] *= fix[0];
       o[n][2] *= fix[1]; o[n][3] *= fix[1];
     }
-    // O += P C: the weights go from the accumulators' layout straight into the A operand's
+    // O += P C: the weights go from the accumulators' layout straight into the A operand's; the latents are read as they
+    // lie, [key][entry], and turned into the B operand's layout by ldmatrix (.trans), two 8-column tiles a load
 #pragma unroll
     for (int kb = 0; kb < 2; ++kb) {
       uint32_t a[4];
@@ -227,12 +248,19 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
       a[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
       a[2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
       a[3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
+      // lane i gives the address of row (i % 8) of matrix i / 8: keys 0..7 and 8..15 of the block, for tile n and n + 1
+      const bf16* rowp = tK + (size_t)(kb * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * qs + chunk0 + (lane >> 4) * 8;
 #pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        const uint32_t* vr = reinterpret_cast<const uint32_t*>(sVt + (size_t)(n * 8 + g) * LM_VT);
-        mma_bf16(o[n], a, vr[kb * 8 + t], vr[kb * 8 + 4 + t]);
+      for (int n = 0; n < NT; n += 2) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"((uint32_t)__cvta_generic_to_shared(rowp + n * 8)));
+        mma_bf16(o[n], a, b0, b1);
+        mma_bf16(o[n + 1], a, b2, b3);
       }
     }
+    __syncthreads();            // the buffer may be filled again
   }
   // results: thread (g, t) holds pairs g and g + 8 of the warp, latent columns chunk0 + 8 n + 2 t + {0, 1}
 #pragma unroll
@@ -325,7 +353,9 @@ extern "C" int tl_attention_latent_mma(const float* q, const void* cache, const 
   const int nt_all = ceil_div(L, 8);
   const int nt = nt_all <= 4 ? 4 : nt_all <= 8 ? 8 : nt_all <= 16 ? 16 : 32;
   const int chunks = ceil_div(nt_all, nt);
-  const size_t smem = ((size_t)(LM_ROWS + LM_KEYS) * p.qs + (size_t)nt * 8 * LM_VT) * sizeof(bf16);
+  // (the second product reads whole 8-column tiles of a chunk, which may reach past a row's end into the next row or, behind
+  // the last row, into the slack: those columns of the result are never stored)
+  const size_t smem = ((size_t)(LM_ROWS + 2 * LM_KEYS) * p.qs + 8 * 32 + 256) * sizeof(bf16);
   TL_REQUIRE(smem <= 200 * 1024, "latent attention: keys of %d entries need %zu bytes of shared memory", Dk, smem);
   const dim3 grid(tiles, chunks, n_spans);
 #define TL_LM(NT_)                                                                                                      \

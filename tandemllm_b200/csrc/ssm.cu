@@ -16,6 +16,12 @@
 
 namespace tl {
 
+// four bytes from global to shared memory without a register in between; the caller commits and waits for the group
+__device__ __forceinline__ void copy_async4(float* to_shared, const float* from_global) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(to_shared)), "l"(from_global)
+               : "memory");
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 
@@ -97,13 +103,11 @@ constexpr int SCAN_TOKENS = 16;     // tokens staged at a time
 // time, else entries lane, lane + 8, ...
 template <int NPER, bool VEC>
 __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanParams p) {
+  // Two buffers of 16 tokens each: while one is computed on, the next 16 tokens' B, C, x and raw step sizes are on
+  // their way into the other (cp.async), so that the recurrence does not wait for global memory.
   extern __shared__ __align__(16) float sm[];
   const int N = p.N, P = p.P;
-  float* sB = sm;                                   // [TOKENS][N]
-  float* sC = sB + SCAN_TOKENS * N;                 // [TOKENS][N]
-  float* sX = sC + SCAN_TOKENS * N;                 // [TOKENS][COLS]
-  float* sDt = sX + SCAN_TOKENS * SCAN_COLS;        // [TOKENS] the step size
-  float* sA = sDt + SCAN_TOKENS;                    // [TOKENS] the decay
+  const int buf_floats = 2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_COLS + 3 * SCAN_TOKENS;
   const int h = blockIdx.y, b = blockIdx.z;
   const int col = threadIdx.x / SCAN_LANES, lane = threadIdx.x % SCAN_LANES;
   const int pcol = blockIdx.x * SCAN_COLS + col;
@@ -135,22 +139,44 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
   const long long xoff = (long long)h * P + (long long)blockIdx.x * SCAN_COLS;
   const long long boff = (long long)p.H * P + (long long)g * N;
   const long long coff = boff + (long long)p.G * N;
-  for (int t0 = 0; t0 < n_rows; t0 += SCAN_TOKENS) {
+  auto stage = [&](int t0, int which) {
+    float* base = sm + which * buf_floats;
+    float* tB = base;
+    float* tC = tB + SCAN_TOKENS * N;
+    float* tX = tC + SCAN_TOKENS * N;
+    float* tRaw = tX + SCAN_TOKENS * SCAN_COLS;
     const int nt = min(SCAN_TOKENS, n_rows - t0);
-    __syncthreads();
     for (int t = 0; t < nt; ++t) {
       const float* src = p.xbc + (long long)(first + t0 + t) * p.ld_xbc;
       for (int n = threadIdx.x; n < N; n += blockDim.x) {
-        sB[t * N + n] = src[boff + n];
-        if (p.mode != 1) sC[t * N + n] = src[coff + n];
+        copy_async4(tB + t * N + n, src + boff + n);
+        if (p.mode != 1) copy_async4(tC + t * N + n, src + coff + n);
       }
     }
     for (int i = threadIdx.x; i < nt * SCAN_COLS; i += blockDim.x) {
       const int t = i / SCAN_COLS, c = i - t * SCAN_COLS;
-      sX[i] = (blockIdx.x * SCAN_COLS + c < P) ? p.xbc[(long long)(first + t0 + t) * p.ld_xbc + xoff + c] : 0.f;
+      if (blockIdx.x * SCAN_COLS + c < P) copy_async4(tX + i, p.xbc + (long long)(first + t0 + t) * p.ld_xbc + xoff + c);
+      else tX[i] = 0.f;
     }
+    if ((int)threadIdx.x < nt) copy_async4(tRaw + threadIdx.x, p.dt + (long long)(first + t0 + threadIdx.x) * p.ld_dt + h);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  stage(0, 0);
+  for (int t0 = 0, which = 0; t0 < n_rows; t0 += SCAN_TOKENS, which ^= 1) {
+    const int nt = min(SCAN_TOKENS, n_rows - t0);
+    const bool more = t0 + SCAN_TOKENS < n_rows;
+    if (more) stage(t0 + SCAN_TOKENS, which ^ 1);       // (the other buffer was last read before the sync that ended the round before)
+    if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    float* sB = sm + which * buf_floats;
+    float* sC = sB + SCAN_TOKENS * N;
+    float* sX = sC + SCAN_TOKENS * N;
+    float* sRaw = sX + SCAN_TOKENS * SCAN_COLS;
+    float* sDt = sRaw + SCAN_TOKENS;
+    float* sA = sDt + SCAN_TOKENS;
     if ((int)threadIdx.x < nt) {
-      const float d = softplus_f(p.dt[(long long)(first + t0 + threadIdx.x) * p.ld_dt + h] + bias);
+      const float d = softplus_f(sRaw[threadIdx.x] + bias);
       sDt[threadIdx.x] = d;
       sA[threadIdx.x] = expf(neg_a * d);
     }
@@ -181,6 +207,7 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
           }
         }
       }
+      __syncthreads();            // the buffer may be filled again
       continue;
     }
     for (int t = 0; t < nt; ++t) {
@@ -223,6 +250,7 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
       acc += __shfl_xor_sync(0xffffffffu, acc, 4);
       if (lane == 0 && live) p.y[(long long)(first + t0 + t) * ((long long)p.H * P) + (long long)h * P + pcol] = fmaf(skip, x, acc);
     }
+    __syncthreads();              // the buffer may be filled again
   }
   if (((p.mode == 0 && p.write_state) || p.mode == 1) && live) {
 #pragma unroll
@@ -330,11 +358,15 @@ extern "C" int tl_ssm_scan(const float* xbc, long long ld_xbc, const float* dt, 
     p.chunk_decay = chunk_scratch + (long long)requests * max_chunks * H * P * N;
   }
   const dim3 grid(ceil_div(P, SCAN_COLS), H, chunked ? requests * max_chunks : requests), block(SCAN_COLS * SCAN_LANES);
-  const size_t smem = (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_COLS + 2 * SCAN_TOKENS) * sizeof(float);
+  const size_t smem = 2 * (size_t)(2 * SCAN_TOKENS * N + SCAN_TOKENS * SCAN_COLS + 3 * SCAN_TOKENS) * sizeof(float);
   const int per = ceil_div(N, SCAN_LANES);
   const bool vec = N % 4 == 0;
 #define TL_SCAN(NPER_)                                                                    \
   do {                                                                                    \
+    if (smem > 48 * 1024) {                                                               \
+      cudaFuncSetAttribute(ssm_scan_kernel<(NPER_ < 4 ? 4 : NPER_), true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cudaFuncSetAttribute(ssm_scan_kernel<NPER_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    }                                                                                     \
     if (vec) ssm_scan_kernel<(NPER_ < 4 ? 4 : NPER_), true><<<grid, block, smem, stream>>>(p); \
     else ssm_scan_kernel<NPER_, false><<<grid, block, smem, stream>>>(p);                 \
   } while (0)
