@@ -368,7 +368,7 @@ class LaunchTimer:
                 "tl_ssm_scan": "state-space recurrence", "tl_causal_conv_act": "causal conv + activation",
                 "tl_conv_state": "causal conv + activation", "tl_gated_group_norm": "gate + norm in parts",
                 "tl_latent_prepare": "latent norm + rotary + cache write", "tl_rmsnorm_rows": "latent norm + rotary + cache write",
-                "tl_head_linear": "products a head", "tl_attention_latent": "latent attention",
+                "tl_head_linear": "products a head", "tl_head_linear_mma": "products a head", "tl_attention_latent_mma": "latent attention", "tl_attention_latent": "latent attention",
                 "tl_add_normed": "norm behind a branch + residual add (+ next norm)", "tl_add_vector": "vector onto the stream", "tl_row_dot": "gate logit a row",
                 "tl_ssm_decode": "conv + state-space recurrence + gate + norm (decode)"}.get(name, name)
 

@@ -48,17 +48,20 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// grid (tiles upper bound, chunks of the latent, spans), 128 threads. NT: 8-column tiles of the latent chunk.
-template <int NT>
-__global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
+// grid (tiles upper bound, chunks of the latent / CPB, spans), 128 CPB threads. NT: 8-column tiles of the latent chunk.
+// CPB: chunks a CTA takes (1 or 2): a second group of four warps runs the same 64 pairs for the next chunk of columns, on
+// the same staged queries and keys.
+template <int NT, int CPB>
+__global__ void __launch_bounds__(128 * CPB) latent_mma_kernel(LatentMmaParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                 // [64][qs]
   bf16* sK = sQ + LM_ROWS * p.qs;                                // two buffers of [32][qs], then some slack (see the launcher)
   __shared__ int s_pos[LM_ROWS], s_lo[LM_ROWS], s_page[2][LM_KEYS];
   __shared__ int s_tile[4];                                      // request, its first row, its rows, first pair of the tile
   const int H = p.H, L = p.L, Dk = p.Dk, qs = p.qs;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int chunk0 = blockIdx.y * NT * 8;
+  const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int chunk_index = blockIdx.y * CPB + (threadIdx.x >> 7);
+  const int chunk0 = chunk_index * NT * 8;
   if (threadIdx.x == 0) {
     int left = blockIdx.x, found = -1;
     for (int b = 0; b < p.requests && found < 0; ++b) {
@@ -286,7 +289,7 @@ __global__ void __launch_bounds__(128) latent_mma_kernel(LatentMmaParams p) {
           const int c = chunk0 + n * 8 + 2 * t + e;
           if (c < L) p.part_o[at * L + c] = o[n][2 * r + e];
         }
-      if (blockIdx.y == 0 && t == 0) {
+      if (chunk_index == 0 && t == 0) {
         p.part_ml[at * 2] = m_run[r];
         p.part_ml[at * 2 + 1] = l_run[r];
       }
@@ -357,17 +360,17 @@ extern "C" int tl_attention_latent_mma(const float* q, const void* cache, const 
   // the last row, into the slack: those columns of the result are never stored)
   const size_t smem = ((size_t)(LM_ROWS + 2 * LM_KEYS) * p.qs + 8 * 32 + 256) * sizeof(bf16);
   TL_REQUIRE(smem <= 200 * 1024, "latent attention: keys of %d entries need %zu bytes of shared memory", Dk, smem);
-  const dim3 grid(tiles, chunks, n_spans);
-#define TL_LM(NT_)                                                                                                      \
+#define TL_LM(NT_, CPB_)                                                                                                \
   do {                                                                                                                  \
     if (smem > 48 * 1024)                                                                                               \
-      cudaFuncSetAttribute(latent_mma_kernel<NT_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);             \
-    latent_mma_kernel<NT_><<<grid, 128, smem, stream>>>(p);                                                             \
+      cudaFuncSetAttribute(latent_mma_kernel<NT_, CPB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    latent_mma_kernel<NT_, CPB_><<<dim3(tiles, chunks / CPB_, n_spans), 128 * CPB_, smem, stream>>>(p);                 \
   } while (0)
-  if (nt == 4) TL_LM(4);
-  else if (nt == 8) TL_LM(8);
-  else if (nt == 16) TL_LM(16);
-  else TL_LM(32);
+  if (nt == 4) TL_LM(4, 1);
+  else if (nt == 8) TL_LM(8, 1);
+  else if (nt == 16) TL_LM(16, 1);
+  else if (chunks == 2) TL_LM(32, 2);
+  else TL_LM(32, 1);
 #undef TL_LM
   TL_LAUNCH_CHECK();
   if (n_spans > 1) {

@@ -87,6 +87,9 @@ def lib():
                                               c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                               c_void_p, c_void_p]
         l.tl_attention_latent_mma.restype = c_int
+        l.tl_head_linear_mma.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong, c_int, c_int,
+                                         c_int, c_int, c_int, c_void_p]
+        l.tl_head_linear_mma.restype = c_int
         l.tl_attention_latent_mma_scratch.argtypes = [c_int, c_int, c_int, c_int]
         l.tl_attention_latent_mma_scratch.restype = c_longlong
         l.tl_tc_set_gate_constants.argtypes = [ctypes.c_float, ctypes.c_float]
@@ -340,6 +343,16 @@ class TensorCore:
             out.data_ptr(),
             ops.ptr(scratch), R, step.n_requests, tiles, H, latent, Dk, n_spans, span, self.status.data_ptr(), ops.stream()),
             "attention_latent_mma", kernels=2 if n_spans > 1 else 1)
+        return True
+
+    def head_linear(self, a, ld_a: int, a_head: int, w, out, ld_out: int, out_head: int, rows: int) -> bool:
+        """out[r, h, n] = sum_k a[r, h, k] w[h, n, k] on the tensor cores (csrc/head_linear_mma.cu) for bfloat16 operands
+        (out bfloat16 or float32); False for anything else."""
+        if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+            return False
+        H, N, K = w.shape
+        _check(lib().tl_head_linear_mma(a.data_ptr(), int(ld_a), int(a_head), w.data_ptr(), out.data_ptr(), int(ld_out),
+                                        int(out_head), rows, H, N, K, ops.dtype_code(out.dtype), ops.stream()), "head_linear_mma")
         return True
 
     def in_proj_conv(self, x, w_in, b_in, taps, b_taps, state, state_slot, req_of_row, positions, y,

@@ -90,13 +90,14 @@ class LatentAttentionMixer(Part):
         qa = torch.empty(R, H, Dk, dtype=torch.float32, device=dev)
         ops.latent_prepare(q, kv, self.w_dkv_norm, self.eps, inv_freq, rot_dims, step.positions, step.req_of_row, table,
                            cache.page_size, cache.k, qa, H, D, L, Rr, rt.status)
-        if D > 0:
+        fast = rt.attention_kernels
+        if D > 0 and (fast is None or not fast.head_linear(q, q.stride(0), D + Rr, self.w_uk_t, qa, H * Dk, Dk, R)):
             ops.head_linear(q, q.stride(0), D + Rr, self.w_uk_t, qa, H * Dk, Dk, R)
         ol = torch.empty(R, H, L, dtype=dt, device=dev)
-        fast = rt.attention_kernels
         if fast is None or not fast.attention_latent(qa, cache, table, step, self.scale, self.window, ol, L, rt):
             ops.attention_latent(qa, cache.k, table, cache.page_size, step.req_of_row, step.positions, self.scale, self.window,
                                  ol, L, rt.status)
         o = torch.empty(R, H * self.vdim, dtype=dt, device=dev)
-        ops.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R)
+        if fast is None or not fast.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R):
+            ops.head_linear(ol, H * L, L, self.w_uv, o, H * self.vdim, self.vdim, R)
         return linear(rt, o, self.w_out, out_dtype=torch.float32, defer=True)
