@@ -65,6 +65,53 @@ __global__ void __launch_bounds__(256) add_normed_kernel(PostNormParams p) {
   }
   const float g = p.delta_gate ? 1.f / (1.f + expf(-p.delta_gate[r])) : 1.f;
   float ss = 0.f;
+  constexpr int CPT = 16;           // columns a thread holds in registers in the form for rows of up to 16 x 256 numbers
+  if (hidden <= CPT * (int)blockDim.x) {
+    // Source by source, a thread's loads of one source all sent before the first is used: a decode step has a handful of
+    // blocks, and their time is the chain of round trips to L2, one a source instead of one a source and column.
+    float d[CPT], routed[CPT];
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) d[i] = routed[i] = 0.f;
+    if (p.delta) {
+      for (int s = 0; s < p.parts; ++s) {
+        const float* src = p.delta + (long long)s * p.part_stride + (size_t)r * hidden;
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) {
+          const int c = threadIdx.x + i * blockDim.x;
+          if (c < hidden) d[i] += src[c];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) d[i] *= g;
+    }
+    if (p.expert_rows) {
+      for (int j = 0; j < p.top_k; ++j) {
+        float v[CPT];
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) v[i] = 0.f;
+        for (int s = 0; s < p.expert_parts; ++s) {
+          const float* src = p.expert_rows + (long long)s * p.expert_part_stride + (long long)s_src[j] * hidden;
+#pragma unroll
+          for (int i = 0; i < CPT; ++i) {
+            const int c = threadIdx.x + i * blockDim.x;
+            if (c < hidden) v[i] += src[c];
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < CPT; ++i) routed[i] = fmaf(s_w[j], v[i], routed[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < CPT; ++i) d[i] = routed[i] + d[i];
+    }
+#pragma unroll
+    for (int i = 0; i < CPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < hidden) {
+        row[c] = d[i];
+        ss += d[i] * d[i];
+      }
+    }
+  } else
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float d = 0.f;
     if (p.delta) {
@@ -109,6 +156,7 @@ __global__ void __launch_bounds__(256) row_dot_kernel(const T* __restrict__ x, l
   if (r >= rows) return;
   const T* xr = x + (long long)r * ld_x;
   float acc = 0.f;
+#pragma unroll 8
   for (int c = lane; c < hidden; c += 32) acc = fmaf(to_f32(xr[c]), to_f32(w[c]), acc);
   acc = warp_sum(acc);
   if (lane == 0) out[r] = acc;
