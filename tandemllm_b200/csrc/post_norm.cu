@@ -33,9 +33,11 @@ struct PostNormParams {
   float pre_eps;
   void* normed;
   const int* gather;
+  int few_rows;              // a step of few rows (few blocks): the form whose loads of a source are all in flight together
 };
 
-template <typename T>
+// FEW: the form for a step of few rows (see `few_rows`), a kernel of its own so that the other keeps its few registers.
+template <typename T, bool FEW>
 __global__ void __launch_bounds__(256) add_normed_kernel(PostNormParams p) {
   extern __shared__ __align__(16) float row[];          // hidden floats, then 33 for the reductions
   float* scratch = row + p.hidden;
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(256) add_normed_kernel(PostNormParams p) {
   const float g = p.delta_gate ? 1.f / (1.f + expf(-p.delta_gate[r])) : 1.f;
   float ss = 0.f;
   constexpr int CPT = 16;           // columns a thread holds in registers in the form for rows of up to 16 x 256 numbers
-  if (hidden <= CPT * (int)blockDim.x) {
+  if (FEW && hidden <= CPT * (int)blockDim.x) {
     // Source by source, a thread's loads of one source all sent before the first is used: a decode step has a handful of
     // blocks, and their time is the chain of round trips to L2, one a source instead of one a source and column.
     float d[CPT], routed[CPT];
@@ -190,14 +192,22 @@ extern "C" int tl_add_normed(float* residual, const float* delta, int parts, lon
   p.expert_rows = expert_rows; p.expert_parts = expert_parts; p.expert_part_stride = expert_part_stride;
   p.pos_of_pair = pos_of_pair; p.ids = ids; p.wts = wts; p.top_k = top_k; p.weight = weight; p.eps = eps; p.hidden = hidden;
   p.pre_weight = pre_weight; p.pre_eps = pre_eps; p.normed = normed; p.gather = gather;
+  p.few_rows = rows <= 2 * sm_count() ? 1 : 0;
   const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+#define TL_ADD_NORMED(T_, FEW_)                                                                                         \
+  do {                                                                                                                  \
+    if (smem > 48 * 1024)                                                                                               \
+      cudaFuncSetAttribute(add_normed_kernel<T_, FEW_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
+    add_normed_kernel<T_, FEW_><<<rows, 256, smem, stream>>>(p);                                                        \
+  } while (0)
   if (dtype == TL_FP32) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_normed_kernel<float><<<rows, 256, smem, stream>>>(p);
+    if (p.few_rows) TL_ADD_NORMED(float, true);
+    else TL_ADD_NORMED(float, false);
   } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(add_normed_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    add_normed_kernel<bf16><<<rows, 256, smem, stream>>>(p);
+    if (p.few_rows) TL_ADD_NORMED(bf16, true);
+    else TL_ADD_NORMED(bf16, false);
   }
+#undef TL_ADD_NORMED
   TL_LAUNCH_CHECK();
   return 0;
 }

@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES) ssm_scan_kernel(ScanPa
   for (int t0 = 0, which = 0; t0 < n_rows; t0 += SCAN_TOKENS, which ^= 1) {
     const int nt = min(SCAN_TOKENS, n_rows - t0);
     const bool more = t0 + SCAN_TOKENS < n_rows;
-    if (more) stage(t0 + SCAN_TOKENS, which ^ 1);       // (the other buffer was last read before the sync that ended the round before)
+    if (more) stage(t0 + SCAN_TOKENS, which ^ 1);       // (the other buffer was last read before the sync that ended the pass before this one)
     if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
     else asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncthreads();
