@@ -408,7 +408,7 @@ def run_schedule(engine, requests, schedule, routes=None):
     return {r: torch.cat(v) for r, v in got.items()}
 
 
-def held_to_the_plain_model(engine, cfg, W, requests, schedule, dtype, what=""):
+def held_to_the_plain_model(engine, cfg, W, requests, schedule, dtype, what="", slack=1.0):
     """Runs the schedule and compares every position of every request. 32-bit: against the plain model as it is (the
     prompts are ones whose every choice of experts is clear of a tie). bfloat16: against the plain model following the
     experts the engine chose."""
@@ -426,7 +426,7 @@ def held_to_the_plain_model(engine, cfg, W, requests, schedule, dtype, what=""):
         # all requests together) are held to the tolerance and every row to ten times that: a fault moves every row by
         # its own size.
         rows = torch.cat(rows)
-        assert float(rows.quantile(0.9)) < TOL[dtype] and float(rows.max()) < 10 * TOL[dtype], what
+        assert float(rows.quantile(0.9)) < slack * TOL[dtype] and float(rows.max()) < 10 * TOL[dtype], what
     return got
 
 
@@ -587,3 +587,74 @@ def test_the_replay_program_on_a_folder(dtype, tmp_path):
     assert rel(a, wx[[0, 24]]) < tol
     assert rel(b, torch.stack([wx[39], wy[18]])) < tol
     assert not (out / "2.f32").exists()
+
+
+def random_config(seed: int) -> dict:
+    """A Puripel configuration drawn from a seed: two to five layers of either kind in any order, sizes from a few numbers
+    up to the ones tensor-core kernels take, with or without a loop, a window, groups of experts, a shared expert, an mlp."""
+    rng = np.random.default_rng(seed)
+    pick = lambda *xs: xs[int(rng.integers(len(xs)))]
+    width = pick(40, 64, 96, 136, 192)
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        mlp = None
+        if rng.random() < 0.85:
+            count = pick(1, 2, 4)
+            per = pick(1, 2, 3, 4)
+            E = count * per
+            keep = int(rng.integers(1, count + 1))
+            top = int(rng.integers(1, min(keep * per, 4) + 1))
+            mlp = C.moe(E, top, pick(8, 24, 64), pick(0.5, 1.5, 7.0), pick(1.0, 2.5), (count, keep) if rng.random() < 0.8 else None,
+                        (pick(16, 40, 128), pick(0.8, 2.0)) if rng.random() < 0.7 else None)
+        if rng.random() < 0.5:
+            groups = pick(1, 2, 4)
+            heads = groups * pick(1, 2, 3)
+            vdim = pick(4, 16, 24, 32, 64)
+            parts = pick(1, 2, heads)
+            layers.append(C.mamba(heads, vdim, pick(1, 8, 16, 32, 48, 128), groups, pick(2, 3, 4), parts, mlp))
+        else:
+            rot = pick(2, 8, 16, 32)
+            layers.append(C.latent(pick(1, 2, 5, 8, 16), pick(8, 16, 32, 64), rot, pick(8, 16, 32), pick(24, 64, 96, 160),
+                                   pick(16, 48, 128), float(rng.uniform(0.05, 0.3)), pick(100.0, 10000.0, 500000.0),
+                                   pick(0, 3, 16, 40, 72, 200), mlp))
+    cfg = {"architecture": "Puripel", "vocab": pick(61, 256, 448, 1000), "width": width, "norm": {"eps": pick(1e-6, 1e-5)},
+           "layers": layers}
+    if rng.random() < 0.7:
+        a = int(rng.integers(0, len(layers)))
+        b = int(rng.integers(a + 1, len(layers) + 1))
+        cfg["loop"] = {"start": a, "stop": b, "times": int(rng.integers(1, 4))}
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_models_drawn_at_random_in_32_bit(seed):
+    """Whole prompt, portions and decoding of a model nobody chose the sizes of, against the plain model, 32-bit."""
+    cfg = random_config(seed)
+    W = C.weights_of(cfg, 100 + seed)
+    engine, cfg, W = engine_of(None, "float32", cfg=cfg, W=W)
+    toks = None
+    for k in range(20):
+        g = torch.Generator().manual_seed(seed * 31 + k)
+        cand = torch.randint(0, cfg["vocab"], (90,), generator=g).tolist()
+        margins = []
+        P.forward(cfg, W, cand, margins=margins)
+        if min(margins, default=math.inf) > 2e-4:
+            toks = cand
+            break
+    assert toks is not None
+    want = P.forward(cfg, W, toks)
+    for sched in ([[("a", 90)]], [[("a", c)] for c in cuts(90, [17, 2, 30, 1])], [[("a", 50)]] + [[("a", 1)]] * 40):
+        got = run_schedule(engine, {"a": toks}, sched)["a"]
+        assert rel(got, want) < TOL["float32"], (seed, len(sched))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_models_drawn_at_random_in_bfloat16(seed):
+    cfg = random_config(seed)
+    W = C.weights_of(cfg, 100 + seed)
+    engine, cfg, W = engine_of(None, "bfloat16", cfg=cfg, W=W)
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, cfg["vocab"], (90,), generator=g).tolist()
+    for sched in ([[("a", 90)]], [[("a", c)] for c in cuts(90, [17, 2, 30, 1])], [[("a", 50)]] + [[("a", 1)]] * 40):
+        # (nobody chose these models for their conditioning: nine rows in ten within twice the tolerance)
+        held_to_the_plain_model(engine, cfg, W, {"a": toks}, sched, "bfloat16", f"seed {seed}", slack=2.0)
